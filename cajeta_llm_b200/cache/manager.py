@@ -49,7 +49,7 @@ class CacheManager:
             need = kv_needs[i]
             if need is None or cache_from[i] is not None:
                 continue
-            spec = GroupSpec(need.kv_heads, need.head_dim, need.window)
+            spec = GroupSpec(need.kv_heads, need.head_dim, need.window, getattr(need, "values", True))
             if spec not in specs:
                 specs.append(spec)
                 plane_count.append(0)
@@ -64,7 +64,7 @@ class CacheManager:
             if self.entry_group[src] is None:
                 raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which caches nothing")
             a, b = kv_needs[i], kv_needs[src]
-            if a is None or (a.kv_heads, a.head_dim) != (b.kv_heads, b.head_dim):
+            if a is None or (a.kv_heads, a.head_dim, getattr(a, "values", True)) != (b.kv_heads, b.head_dim, getattr(b, "values", True)):
                 raise CacheError(f"schedule entry {i} cannot read the cache of entry {src}: head layout differs")
             if b.window > 0 and (a.window == 0 or a.window > b.window):
                 raise CacheError(f"schedule entry {i} (window {a.window}) cannot read the cache of entry {src}, "
@@ -76,13 +76,13 @@ class CacheManager:
         self.group_pages = counts
         self.books = CacheBooks(specs, counts, page_tokens, max_seqs, max_tokens_per_seq)
         self.k: List[torch.Tensor] = []
-        self.v: List[torch.Tensor] = []
+        self.v: List[Optional[torch.Tensor]] = []      # None for a group that keeps no values
         self.state: Dict[int, torch.Tensor] = {}
         if self.device is not None:
             for spec, planes, pages in zip(specs, plane_count, counts):
                 shape = (planes, pages, spec.kv_heads, page_tokens, spec.head_dim)
                 self.k.append(torch.zeros(shape, dtype=cache_dtype, device=self.device))
-                self.v.append(torch.zeros(shape, dtype=cache_dtype, device=self.device))
+                self.v.append(torch.zeros(shape, dtype=cache_dtype, device=self.device) if spec.values else None)
             for i, need in enumerate(state_needs):
                 if need is not None:
                     self.state[i] = torch.zeros((max_seqs,) + tuple(need.shape), dtype=need.dtype, device=self.device)
@@ -136,7 +136,7 @@ class CacheManager:
         if g is None:
             return None, None, None
         p = self.entry_plane[entry]
-        return self.k[g][p], self.v[g][p], g
+        return self.k[g][p], (self.v[g][p] if self.v[g] is not None else None), g
 
     def bytes_per_token(self) -> int:
         """Cache bytes one token occupies over all planes."""
@@ -145,7 +145,7 @@ class CacheManager:
         for g, spec in enumerate(self.group_specs):
             planes = sum(1 for e, gg in enumerate(self.entry_group) if gg == g and self.entry_plane[e] is not None
                          and self._owns(e))
-            total += 2 * planes * spec.kv_heads * spec.head_dim * size
+            total += (2 if spec.values else 1) * planes * spec.kv_heads * spec.head_dim * size
         return total
 
     def _owns(self, entry: int) -> bool:

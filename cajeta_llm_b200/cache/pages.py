@@ -145,6 +145,7 @@ class GroupSpec:
     kv_heads: int
     head_dim: int
     window: int      # 0: every key is kept
+    values: bool = True      # False: one vector per token and head, no plane of values
 
 
 class _GroupPages:

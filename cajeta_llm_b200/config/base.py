@@ -149,10 +149,13 @@ def get_architecture(name: str) -> Architecture:
 
 
 def parse_config_dict(raw: Dict[str, Any], source: str = "config.json") -> ModelConfig:
-    """Choose the configuration class by ``architectures[0]`` and parse the keys."""
+    """Choose the configuration class by ``architectures[0]`` (or, in files that name a
+    single design, by the string ``architecture``) and parse the keys."""
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{source}: required key 'architectures' is missing or is not a list of names")
+        raise ConfigError(f"{source}: required key 'architectures' (a list of names) or 'architecture' (a name) is missing")
     arch = get_architecture(archs[0])
     return arch.config_class.from_reader(ConfigReader(raw, source))
 

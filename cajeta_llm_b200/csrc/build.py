@@ -42,6 +42,8 @@ LIBRARIES: Dict[str, str] = {
     "attention_prefill": "attention_prefill.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "random_fill": "random_fill.cu",
+    "recurrent": "recurrent.cu",
+    "latent_attention": "latent_attention.cu",
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 

@@ -245,8 +245,9 @@ def _pin_and_gap(pin: Optional[torch.Tensor], gap: Optional[torch.Tensor], T: in
 
 def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[torch.Tensor], top_k: int,
                 norm_topk: bool, sel: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor],
-                pin: Optional[torch.Tensor] = None, gap: Optional[torch.Tensor] = None) -> None:
-    """Router logits, softmax over all experts, top-k and the shared expert's sigmoid gate.
+                pin: Optional[torch.Tensor] = None, gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False) -> None:
+    """Router logits, softmax over all experts (or, with ``sigmoid_scores``, each expert's own
+    sigmoid), top-k and the shared expert's sigmoid gate.
     ``pin`` (int32 [T, k]): the experts are given, not chosen; the weights are still the row's own
     probabilities of them.  ``gap`` (float32 [T], not with ``pin``): each row's routing margin
     (p_k - p_{k+1}) / p_k out."""
@@ -264,8 +265,8 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
     if tickets is None:
         tickets = _router_tickets[x.device] = torch.zeros((4,), dtype=torch.int32, device=x.device)
     st = library("moe_route").cj_router_topk(_ptr(x), _ptr(router_w), _ptr(shared_gate), _i(T), _i(H), _i(E), _i(top_k),
-                                             _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights), _ptr(shared_scale),
-                                             _ptr(logits), _ptr(tickets), _ptr(pin), _ptr(gap), _stream())
+                                             _i((1 if norm_topk else 0) | (2 if sigmoid_scores else 0)), _ptr(sel), _ptr(weights),
+                                             _ptr(shared_scale), _ptr(logits), _ptr(tickets), _ptr(pin), _ptr(gap), _stream())
     _check(st, "router_topk")
     if T > 32:
         global launches
@@ -274,7 +275,7 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
 
 def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_topk: bool, sel: torch.Tensor,
                   weights: torch.Tensor, shared_scale: Optional[torch.Tensor], pin: Optional[torch.Tensor] = None,
-                  gap: Optional[torch.Tensor] = None) -> None:
+                  gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False) -> None:
     """Softmax over all experts, top-k and the shared gate's sigmoid from router logits given
     as partial sums ``[S, T, ld]`` (float32; column ``num_experts`` holds the gate's dot when
     ``shared_scale`` is given); the partials of a row are added in order first."""
@@ -288,8 +289,8 @@ def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_top
     if shared_scale is not None:
         _need(shared_scale, "shared_scale", torch.float32)
     st = library("moe_route").cj_router_select(_ptr(partials), _i(S), _ll(partials.stride(0)), _i(ld), _i(T), _i(num_experts),
-                                               _i(top_k), _i(1 if norm_topk else 0), _ptr(sel), _ptr(weights),
-                                               _ptr(shared_scale), _ptr(pin), _ptr(gap), _stream())
+                                               _i(top_k), _i((1 if norm_topk else 0) | (2 if sigmoid_scores else 0)), _ptr(sel),
+                                               _ptr(weights), _ptr(shared_scale), _ptr(pin), _ptr(gap), _stream())
     _check(st, "router_select")
 
 
@@ -325,6 +326,173 @@ def moe_combine(hs: torch.Tensor, y: Optional[torch.Tensor], slot_of_pick: Optio
     st = library("rowwise").cj_moe_combine(_ptr(hs), _ptr(y), _ptr(slot_of_pick), _ptr(weights), _i(top_k), _ptr(shared),
                                            _i(chunks), _ll(stride), _ptr(shared_scale), _i(T), _i(H), _stream())
     _check(st, "moe_combine")
+
+
+# -- a block that norms a sublayer's output; mixers with a state per request -----------------------------
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x in out's dtype; x float32."""
+    _need(x, "x", torch.float32), _need(out, "out")
+    if out.numel() != x.numel():
+        raise KernelError("cast_rows: sizes differ")
+    _check(library("recurrent").cj_cast_rows(_ptr(x), _ptr(out), _i(_code(out)), _ll(x.numel()), _stream()), "cast_rows")
+
+
+def rmsnorm_add(hs: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """hs[r] += y[r] / sqrt(mean(y[r]^2) + eps) * weight; everything float32."""
+    _need(hs, "hs", torch.float32), _need(y, "y", torch.float32), _need(weight, "weight", torch.float32)
+    rows, H = hs.shape
+    if y.shape != hs.shape or weight.numel() != H:
+        raise KernelError(f"rmsnorm_add: shapes hs {tuple(hs.shape)} y {tuple(y.shape)} weight {tuple(weight.shape)} do not agree")
+    _check(library("recurrent").cj_rmsnorm_add(_ptr(hs), _ptr(y), _ptr(weight), _f(eps), _i(rows), _i(H), _stream()), "rmsnorm_add")
+
+
+def scale_rows_gather(x: torch.Tensor, slot_of_pick: torch.Tensor, weights: torch.Tensor, top_k: int, out: torch.Tensor) -> None:
+    """out[slot_of_pick[t, j]] = weights[t, j] * x[t]: the rows of a mixture's grouped product when
+    a pick's score multiplies the expert's input.  x float32 [T, H]; out [T * k, H]."""
+    _need(x, "x", torch.float32), _need(slot_of_pick, "slot_of_pick", torch.int32), _need(weights, "weights", torch.float32)
+    _need(out, "out")
+    T, H = x.shape
+    if slot_of_pick.numel() != T * top_k or weights.numel() != T * top_k or out.shape != (T * top_k, H):
+        raise KernelError("scale_rows_gather: sizes do not agree")
+    st = library("recurrent").cj_scale_rows_gather(_ptr(x), _ptr(slot_of_pick), _ptr(weights), _i(T * top_k), _i(top_k), _i(H),
+                                                   _ptr(out), _i(_code(out)), _stream())
+    _check(st, "scale_rows_gather")
+
+
+def short_conv(x: torch.Tensor, x_offset: int, channels: int, taps: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+               state: torch.Tensor, row_req: torch.Tensor, req_start: torch.Tensor, req_slot: torch.Tensor,
+               out: torch.Tensor, activate: bool = True) -> None:
+    """Causal convolution per channel over columns [x_offset, x_offset + channels) of x (float32 [T, ld]):
+    out[r, c] = act(bias[c] + sum_j weight[c, taps-1-j] * x[r - j, c]), where rows before the
+    request's first row of this step come from ``state`` ([slots, n] float32, whose first
+    (taps-1) * channels entries per slot are the request's last inputs, oldest first)."""
+    _need(x, "x", torch.float32), _need(weight, "weight", torch.float32), _need(state, "state", torch.float32), _need(out, "out")
+    for n, t in (("row_req", row_req), ("req_start", req_start), ("req_slot", req_slot)):
+        _need(t, n, torch.int32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    if weight.shape != (channels, taps) or x.shape[1] < x_offset + channels or out.shape[1] < channels or state[0].numel() < (taps - 1) * channels:
+        raise KernelError("short_conv: sizes do not agree")
+    st = library("recurrent").cj_short_conv(ctypes.c_void_p(x.data_ptr() + 4 * x_offset), _i(x.stride(0)), _i(channels), _i(taps), _ptr(weight), _ptr(bias), _ptr(state),
+                                            _ll(state.stride(0)), _ptr(row_req), _ptr(req_start), _ptr(req_slot), _ptr(out),
+                                            _i(out.stride(0)), _i(_code(out)), _i(1 if activate else 0), _i(x.shape[0]), _stream())
+    _check(st, "short_conv")
+
+
+def short_conv_commit(x: torch.Tensor, x_offset: int, channels: int, taps: int, state: torch.Tensor, req_start: torch.Tensor,
+                      req_slot: torch.Tensor, requests: int) -> None:
+    """After ``short_conv``: every request's last taps-1 inputs (of this step, and of the state
+    where the step brought fewer) become its state."""
+    _need(x, "x", torch.float32), _need(state, "state", torch.float32)
+    _need(req_start, "req_start", torch.int32), _need(req_slot, "req_slot", torch.int32)
+    if taps <= 1:
+        return
+    st = library("recurrent").cj_short_conv_commit(ctypes.c_void_p(x.data_ptr() + 4 * x_offset), _i(x.stride(0)), _i(channels), _i(taps), _ptr(state),
+                                                   _ll(state.stride(0)), _ptr(req_start), _ptr(req_slot), _i(requests), _stream())
+    _check(st, "short_conv_commit")
+
+
+SCAN_SSD, SCAN_DELTA = 0, 1
+
+
+def state_scan(mode: int, x: torch.Tensor, off_a: int, off_b: int, off_v: int, raw: torch.Tensor, off_dt: int, off_beta: int,
+               A_log: torch.Tensor, dt_bias: torch.Tensor, skip: Optional[torch.Tensor], state: torch.Tensor, state_offset: int,
+               req_start: torch.Tensor, req_slot: torch.Tensor, out: torch.Tensor, requests: int, heads: int, groups: int,
+               rows: int, cols: int, q_scale: float = 1.0) -> None:
+    """Walks every request's rows of the step in order through its recurrent state
+    (``state[slot, state_offset:]`` seen as [heads, rows, cols] float32) and writes a row's
+    read-out to ``out`` [T, heads * cols].
+
+    ``SCAN_SSD``: x columns off_a = B [groups, rows], off_b = C, off_v = x [heads, cols]; raw column
+    off_dt + h = the step size before softplus.  S = exp(-exp(A_log) dt) S + dt B x^T; y = S^T C + skip x.
+    ``SCAN_DELTA``: off_a = q [groups, rows], off_b = k, off_v = v; raw columns off_dt + h (decay input)
+    and off_beta + h.  q and k become unit vectors (q times ``q_scale``); S = g S; u = beta (v - S^T k);
+    S += k u^T; o = S^T q."""
+    _need(x, "x", torch.float32), _need(raw, "raw", torch.float32), _need(state, "state", torch.float32), _need(out, "out", torch.float32)
+    _need(A_log, "A_log", torch.float32), _need(dt_bias, "dt_bias", torch.float32)
+    _need(req_start, "req_start", torch.int32), _need(req_slot, "req_slot", torch.int32)
+    if skip is not None:
+        _need(skip, "skip", torch.float32)
+    if state[0].numel() < state_offset + heads * rows * cols or out.shape[1] != heads * cols:
+        raise KernelError("state_scan: state or out too small")
+    st = library("recurrent").cj_state_scan(
+        _i(mode), _ptr(x), _i(x.stride(0)), _i(off_a), _i(off_b), _i(off_v), _ptr(raw), _i(raw.stride(0)), _i(off_dt), _i(off_beta),
+        _ptr(A_log), _ptr(dt_bias), _ptr(skip), ctypes.c_void_p(state.data_ptr() + 4 * state_offset), _ll(state.stride(0)),
+        _ptr(req_start), _ptr(req_slot), _ptr(out), _i(requests), _i(heads), _i(groups), _i(rows), _i(cols), _f(q_scale), _stream())
+    _check(st, "state_scan")
+
+
+def gated_group_norm(y: torch.Tensor, part_len: int, z: torch.Tensor, z_offset: int, weight: torch.Tensor, eps: float,
+                     gate_first: bool, out: torch.Tensor) -> None:
+    """Rows of y (float32 [T, n]) in parts of ``part_len``: RMS norm of each part times weight
+    (indexed by column modulo its length) and times silu(z[:, z_offset + column]); the gate is
+    applied before the norm's statistics when ``gate_first``, after the norm otherwise."""
+    _need(y, "y", torch.float32), _need(z, "z", torch.float32), _need(weight, "weight", torch.float32), _need(out, "out")
+    T, n = y.shape
+    if out.shape != y.shape or z.shape[1] < z_offset + n:
+        raise KernelError("gated_group_norm: sizes do not agree")
+    st = library("recurrent").cj_gated_group_norm(_ptr(y), _i(n), _i(part_len), ctypes.c_void_p(z.data_ptr() + 4 * z_offset),
+                                                  _i(z.stride(0)), _ptr(weight), _i(weight.numel()), _f(eps),
+                                                  _i(1 if gate_first else 0), _ptr(out), _i(_code(out)), _i(T), _stream())
+    _check(st, "gated_group_norm")
+
+
+# -- attention over a compressed latent ---------------------------------------------------------------
+def latent_kv_write(d: torch.Tensor, d_offset: int, rank: int, rot: int, rotary: int, weight: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor],
+                    positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
+                    plane: torch.Tensor) -> None:
+    """Columns [d_offset, d_offset + rank + rot) of d (float32): the RMS-normed latent (times weight) and
+    the key part, its first ``rotary`` entries rotated in pairs (2i, 2i+1), go to the row's place in
+    the paged cache (entries of rank + rot)."""
+    _need(d, "d", torch.float32), _need(weight, "weight", torch.float32), _need(plane, "plane")
+    _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+    if d.shape[1] < d_offset + rank + rot or plane.shape[-1] != rank + rot:
+        raise KernelError("latent_kv_write: sizes do not agree")
+    st = library("latent_attention").cj_latent_kv_write(ctypes.c_void_p(d.data_ptr() + 4 * d_offset), _i(d.stride(0)), _i(rank), _i(rot), _i(rotary), _ptr(weight), _f(eps),
+                                                        _ptr(inv_freq), _ptr(positions), _ptr(row_req), _ptr(table),
+                                                        _i(table.stride(0)), _i(page_tokens), _ptr(plane), _i(_code(plane)),
+                                                        _i(d.shape[0]), _stream())
+    _check(st, "latent_kv_write")
+
+
+def latent_q_split(q: torch.Tensor, heads: int, dim: int, rot: int, rotary: int, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+                   q_plain: torch.Tensor, q_rot: torch.Tensor) -> None:
+    """q float32 [T, >= heads * (dim + rot)] -> q_plain [heads, T, dim] and the rotated parts q_rot float32 [T, heads, rot]."""
+    _need(q, "q", torch.float32), _need(q_plain, "q_plain"), _need(q_rot, "q_rot", torch.float32), _need(positions, "positions", torch.int32)
+    T = q.shape[0]
+    if q_plain.numel() != heads * T * dim or q_rot.numel() != T * heads * rot:
+        raise KernelError("latent_q_split: sizes do not agree")
+    st = library("latent_attention").cj_latent_q_split(_ptr(q), _i(q.stride(0)), _i(heads), _i(dim), _i(rot), _i(rotary), _ptr(inv_freq),
+                                                       _ptr(positions), _i(T), _ptr(q_plain), _i(_code(q_plain)), _ptr(q_rot), _stream())
+    _check(st, "latent_q_split")
+
+
+def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tensor, rank: int, rot: int, heads: int,
+                     positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int, scale: float,
+                     out: torch.Tensor) -> None:
+    """Every (row, head): softmax over the row's keys [0, position] of (q_abs . c + q_rot . r) * scale,
+    and the weighted sum of the latents.  q_abs float32 [heads, T, rank]; q_rot float32 [T, heads, rot];
+    out [heads, T, rank] in the cache's dtype."""
+    _need(q_abs, "q_abs", torch.float32), _need(q_rot, "q_rot", torch.float32), _need(plane, "plane"), _need(out, "out", plane.dtype)
+    _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+    T = positions.numel()
+    if q_abs.numel() != heads * T * rank or out.numel() != heads * T * rank or plane.shape[-1] != rank + rot:
+        raise KernelError("latent_attention: sizes do not agree")
+    st = library("latent_attention").cj_latent_attention(_ptr(q_abs), _ptr(q_rot), _ptr(plane), _i(_code(plane)), _i(rank), _i(rot),
+                                                         _i(heads), _i(T), _ptr(positions), _ptr(row_req), _ptr(table),
+                                                         _i(table.stride(0)), _i(page_tokens), _f(scale), _ptr(out), _stream())
+    _check(st, "latent_attention")
+
+
+def latent_gate_out(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:
+    """out[t, h, :] = o[h, t, :] * sigmoid(gate[t, gate_offset + h]); o float32 [heads, T, vdim], gate float32."""
+    _need(o, "o", torch.float32), _need(gate, "gate", torch.float32), _need(out, "out")
+    T = out.shape[0]
+    if o.numel() != heads * T * vdim or out.shape[1] != heads * vdim:
+        raise KernelError("latent_gate_out: sizes do not agree")
+    st = library("latent_attention").cj_latent_gate_out(_ptr(o), ctypes.c_void_p(gate.data_ptr() + 4 * gate_offset), _i(gate.stride(0)),
+                                                        _i(heads), _i(vdim), _i(T), _ptr(out), _i(_code(out)), _stream())
+    _check(st, "latent_gate_out")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

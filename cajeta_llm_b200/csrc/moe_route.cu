@@ -108,17 +108,25 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
                                            float* __restrict__ w, float* __restrict__ shared_scale, float* probs, int lane,
                                            const int* __restrict__ pin, float* __restrict__ gap) {
     if (shared_scale && lane == 0) shared_scale[t] = 1.0f / (1.0f + expf(-row[E]));
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
-    mx = warp_max(mx);
-    float sum = 0.0f;
-    for (int e = lane; e < E; e += 32) {
-        float p = expf(row[e] - mx);
-        probs[e] = p;
-        sum += p;
+    // bit 1 of norm_topk: an expert's score is the sigmoid of its own logit instead of the
+    // softmax over all experts (bit 0 still asks for the picked scores to be renormalised)
+    const bool sigmoid_scores = (norm_topk & 2) != 0;
+    norm_topk &= 1;
+    if (sigmoid_scores) {
+        for (int e = lane; e < E; e += 32) probs[e] = 1.0f / (1.0f + expf(-row[e]));
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) {
+            float p = expf(row[e] - mx);
+            probs[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
     }
-    sum = warp_sum(sum);
-    for (int e = lane; e < E; e += 32) probs[e] = probs[e] / sum;
     __syncwarp();
 
     if (pin) {

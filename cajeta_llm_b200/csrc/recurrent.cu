@@ -1,0 +1,377 @@
+// Mixers that carry a fixed-size state per request instead of a growing cache, and the
+// row-wise kernels of a block that norms a sublayer's OUTPUT.  Everything that enters a
+// recurrence is float32: the state, decays and their logarithms, step sizes, gates, unit
+// norms.  A step's rows are laid out request after request; every kernel finds a row's
+// request, the request's first row and its state slot in the step's device metadata
+// (row_req, req_start, req_slot), so the same launch serves prompt portions of any length
+// beside single decoded tokens, and a request that a captured step is filled up with
+// (slot -1, no rows) is left alone.
+//
+//   cast_rows          float32 rows -> the activation dtype (a sublayer reads the stream itself)
+//   rmsnorm_add        hs += y / sqrt(mean(y^2) + eps) * w
+//   scale_rows_gather  out[slot] = weight[pick] * x[token]  (a mixture whose score multiplies the expert's INPUT)
+//   short_conv         causal convolution per channel over time (+ bias, + SiLU) whose first
+//                      taps-1 inputs come from the request's state; short_conv_commit then
+//                      stores the step's last taps-1 inputs
+//   ssd_scan           S_t = exp(-A dt) S_(t-1) + dt B_t x_t^T ;  y_t = S_t^T C_t + D x_t
+//   delta_scan         S <- g S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q
+//   gated_group_norm   y * silu(z) and RMS over equal parts of a row, in either order
+//
+// The two scans give a thread one column of the state (one value dimension) for a share of
+// its rows: a block is (request, head, tile of columns), a column's rows are dealt to DP
+// neighbouring lanes, each holding NPER of them in registers, and a sum over the rows is a
+// butterfly over those lanes.  Columns never talk to each other, so a block needs no
+// barrier; the tokens of a request are walked in order, which is what makes the result
+// independent of how a prompt was cut: the state after token t is the same sequence of
+// float32 operations whether t ended a step or not.
+#include "common.cuh"
+
+using namespace cj;
+
+namespace {
+
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < nw; ++i) t += scratch[i];
+    return t;
+}
+
+template <typename TO>
+__global__ void cast_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, long long n) {
+    cj::after_predecessor();
+    cj::release_successor();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(x[i]);
+}
+
+__global__ void rmsnorm_add_kernel(float* __restrict__ hs, const float* __restrict__ y, const float* __restrict__ w, float eps, int H) {
+    cj::after_predecessor();
+    cj::release_successor();
+    __shared__ float scratch[32];
+    const float* src = y + (size_t)blockIdx.x * H;
+    float* dst = hs + (size_t)blockIdx.x * H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] += src[i] * scale * w[i];
+}
+
+template <typename TO>
+__global__ void scale_rows_gather_kernel(const float* __restrict__ x, const int* __restrict__ slot_of_pick,
+                                         const float* __restrict__ weight, int k, int H, TO* __restrict__ out) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int pick = blockIdx.x;
+    const float* src = x + (size_t)(pick / k) * H;
+    TO* dst = out + (size_t)slot_of_pick[pick] * H;
+    const float wt = weight[pick];
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = from_f32<TO>(wt * src[i]);
+}
+
+// ---------------------------------------------------------------------------------
+// short convolution over time with the request's last taps-1 inputs as state
+// state of a slot: [taps-1][C] float32, oldest first
+// ---------------------------------------------------------------------------------
+template <typename TO>
+__global__ void short_conv_kernel(const float* __restrict__ in, int ld_in, int C, int taps, const float* __restrict__ w,
+                                  const float* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
+                                  const int* __restrict__ row_req, const int* __restrict__ req_start,
+                                  const int* __restrict__ req_slot, TO* __restrict__ out, int ld_out, int act) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int r = blockIdx.x;
+    const int req = row_req[r];
+    const int t = r - req_start[req];
+    const int slot = req_slot[req];
+    const float* st = state + (size_t)slot * slot_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc = bias ? bias[c] : 0.0f;
+        for (int j = taps - 1; j >= 0; --j) {          // oldest input first
+            const int src_t = t - j;
+            const float v = src_t >= 0 ? in[(size_t)(r - j) * ld_in + c] : st[(size_t)(taps - 1 + src_t) * C + c];
+            acc = fmaf(w[(size_t)c * taps + (taps - 1 - j)], v, acc);
+        }
+        if (act) acc = acc / (1.0f + expf(-acc));
+        out[(size_t)r * ld_out + c] = from_f32<TO>(acc);
+    }
+}
+
+__global__ void short_conv_commit_kernel(const float* __restrict__ in, int ld_in, int C, int taps, float* __restrict__ state,
+                                         long long slot_stride, const int* __restrict__ req_start,
+                                         const int* __restrict__ req_slot) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int req = blockIdx.x;
+    const int slot = req_slot[req];
+    const int first = req_start[req], n = req_start[req + 1] - first;
+    if (slot < 0 || n <= 0) return;
+    float* st = state + (size_t)slot * slot_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        // ascending k: an entry that is kept moves down from k + n, which is read before it is written
+        for (int k = 0; k < taps - 1; ++k) {
+            const int src_t = n - (taps - 1) + k;
+            st[(size_t)k * C + c] = src_t >= 0 ? in[(size_t)(first + src_t) * ld_in + c] : st[(size_t)(k + n) * C + c];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// the scans
+// ---------------------------------------------------------------------------------
+struct ScanArgs {
+    const float* x;      // the step's rows after convolution and activation, [T, ld]
+    int ld;
+    int off_a, off_b, off_v;   // ssd: B, C, x ; delta: q, k, v  (column offsets in x)
+    const float* raw;    // the step's rows of the plain projections, [T, ld_raw]
+    int ld_raw;
+    int off_dt, off_beta;      // ssd: dt ; delta: the decay's input a, beta's input b
+    const float* A_log; const float* dt_bias; const float* skip;    // per head (skip: ssd's D)
+    float* state; long long slot_stride;     // per slot [heads][rows][cols] float32
+    const int* req_start; const int* req_slot;
+    float* out;          // [T, heads * cols]
+    int heads, groups, rows, cols;           // rows: state rows (N or key dim); cols: value dim
+    float q_scale;
+};
+
+template <int NPER, bool DELTA>
+__global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int req = blockIdx.x, head = blockIdx.y;
+    const int slot = p.req_slot[req];
+    const int first = p.req_start[req], n = p.req_start[req + 1] - first;
+    if (slot < 0 || n <= 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cols_per_warp = 32 / DP;
+    const int part = lane / cols_per_warp;                  // which share of the state's rows
+    const int col = blockIdx.z * (4 * cols_per_warp) + warp * cols_per_warp + (lane % cols_per_warp);
+    const bool live = col < p.cols;
+    const int group = head / (p.heads / p.groups);
+    float* S = p.state + (size_t)slot * p.slot_stride + (size_t)head * p.rows * p.cols;
+    float s[NPER];
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+        const int d = part + DP * i;
+        s[i] = (live && d < p.rows) ? S[(size_t)d * p.cols + col] : 0.0f;
+    }
+    const float A = expf(p.A_log[head]);
+    const float bias = p.dt_bias[head];
+    const float skip = DELTA ? 0.0f : p.skip[head];
+    for (int t = 0; t < n; ++t) {
+        const float* xr = p.x + (size_t)(first + t) * p.ld;
+        const float* rr = p.raw + (size_t)(first + t) * p.ld_raw;
+        const float* ra = xr + p.off_a + group * p.rows;
+        const float* rb = xr + p.off_b + group * p.rows;
+        const float xv = live ? xr[p.off_v + head * p.cols + col] : 0.0f;
+        float a[NPER], b[NPER];
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+            const int d = part + DP * i;
+            a[i] = d < p.rows ? ra[d] : 0.0f;
+            b[i] = d < p.rows ? rb[d] : 0.0f;
+        }
+        if (DELTA) {
+            // a = q, b = k: unit vectors per head, q also times rows^(-1/2)
+            float qq = 0.0f, kk = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NPER; ++i) { qq = fmaf(a[i], a[i], qq); kk = fmaf(b[i], b[i], kk); }
+            for (int o = cols_per_warp; o < 32; o <<= 1) {
+                qq += __shfl_xor_sync(0xffffffffu, qq, o);
+                kk += __shfl_xor_sync(0xffffffffu, kk, o);
+            }
+            const float qs = p.q_scale / sqrtf(qq + 1e-6f), ks = 1.0f / sqrtf(kk + 1e-6f);
+            const float decay = expf(-A * softplus_f(rr[p.off_dt + head] + bias));
+            const float beta = sigmoid_f(rr[p.off_beta + head]);
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NPER; ++i) {
+                a[i] *= qs;
+                b[i] *= ks;
+                s[i] *= decay;
+                dot = fmaf(s[i], b[i], dot);
+            }
+            for (int o = cols_per_warp; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            const float u = beta * (xv - dot);
+            float y = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NPER; ++i) {
+                s[i] = fmaf(b[i], u, s[i]);
+                y = fmaf(s[i], a[i], y);
+            }
+            for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = y;
+        } else {
+            // a = B, b = C
+            const float dt = softplus_f(rr[p.off_dt + head] + bias);
+            const float decay = expf(-A * dt);
+            const float dx = dt * xv;
+            float y = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NPER; ++i) {
+                s[i] = fmaf(decay, s[i], a[i] * dx);
+                y = fmaf(s[i], b[i], y);
+            }
+            for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = fmaf(skip, xv, y);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+        const int d = part + DP * i;
+        if (live && d < p.rows) S[(size_t)d * p.cols + col] = s[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// y * silu(z) and an RMS over equal parts of the row, in either order:
+//   gate_first:  v = y * silu(z);  out = v / rms_part(v) * w
+//   else:        out = y / rms_part(y) * w * silu(z)
+// w has w_len entries and is indexed by (column % w_len): a weight per column of the row,
+// or one shared by all parts.  One warp per part.
+// ---------------------------------------------------------------------------------
+template <typename TO>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, int n, int part_len, const float* __restrict__ z, int ld_z,
+                                        const float* __restrict__ w, int w_len, float eps, int gate_first,
+                                        TO* __restrict__ out) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int parts = n / part_len;
+    for (int g = blockIdx.y * nw + warp; g < parts; g += gridDim.y * nw) {
+        const float* yr = y + (size_t)r * n + (size_t)g * part_len;
+        const float* zr = z + (size_t)r * ld_z + (size_t)g * part_len;
+        float ss = 0.0f;
+        for (int i = lane; i < part_len; i += 32) {
+            float v = yr[i];
+            if (gate_first) { const float zz = zr[i]; v *= zz / (1.0f + expf(-zz)); }
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)part_len + eps);
+        for (int i = lane; i < part_len; i += 32) {
+            const float zz = zr[i];
+            const float gate = zz / (1.0f + expf(-zz));
+            const int c = g * part_len + i;
+            float v = yr[i];
+            v = gate_first ? (v * gate) * scale * w[c % w_len] : v * scale * w[c % w_len] * gate;
+            out[(size_t)r * n + c] = from_f32<TO>(v);
+        }
+    }
+}
+
+}  // namespace
+
+CJ_EXPORT int cj_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!x || !out) return CJ_ERR_ARG;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_dtype == CJ_F32) cj::launch(cast_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, x, (float*)out, n);
+    else if (out_dtype == CJ_BF16) cj::launch(cast_rows_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, x, (__nv_bfloat16*)out, n);
+    else return CJ_ERR_DTYPE;
+    return launch_status();
+}
+
+CJ_EXPORT int cj_rmsnorm_add(float* hs, const float* y, const float* w, float eps, int rows, int H, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!hs || !y || !w || H <= 0) return CJ_ERR_ARG;
+    int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    cj::launch(rmsnorm_add_kernel, dim3(rows), dim3(threads), 0, stream, hs, y, w, eps, H);
+    return launch_status();
+}
+
+CJ_EXPORT int cj_scale_rows_gather(const float* x, const int* slot_of_pick, const float* weight, int picks, int k, int H,
+                                   void* out, int out_dtype, cudaStream_t stream) {
+    if (picks <= 0) return 0;
+    if (!x || !slot_of_pick || !weight || !out || k < 1 || H <= 0) return CJ_ERR_ARG;
+    int threads = H >= 1024 ? 256 : 128;
+    if (out_dtype == CJ_F32) cj::launch(scale_rows_gather_kernel<float>, dim3(picks), dim3(threads), 0, stream, x, slot_of_pick, weight, k, H, (float*)out);
+    else if (out_dtype == CJ_BF16) cj::launch(scale_rows_gather_kernel<__nv_bfloat16>, dim3(picks), dim3(threads), 0, stream, x, slot_of_pick, weight, k, H, (__nv_bfloat16*)out);
+    else return CJ_ERR_DTYPE;
+    return launch_status();
+}
+
+CJ_EXPORT int cj_short_conv(const float* in, int ld_in, int C, int taps, const float* w, const float* bias, const float* state,
+                            long long slot_stride, const int* row_req, const int* req_start, const int* req_slot, void* out,
+                            int ld_out, int out_dtype, int act, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!in || !w || !state || !row_req || !req_start || !req_slot || !out || C <= 0 || taps < 1) return CJ_ERR_ARG;
+    int threads = C >= 512 ? 256 : 128;
+    int by = (C + threads - 1) / threads;
+    if (by > 64) by = 64;
+    dim3 grid(T, by);
+    if (out_dtype == CJ_F32) cj::launch(short_conv_kernel<float>, grid, dim3(threads), 0, stream, in, ld_in, C, taps, w, bias, state, slot_stride, row_req, req_start, req_slot, (float*)out, ld_out, act);
+    else if (out_dtype == CJ_BF16) cj::launch(short_conv_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, in, ld_in, C, taps, w, bias, state, slot_stride, row_req, req_start, req_slot, (__nv_bfloat16*)out, ld_out, act);
+    else return CJ_ERR_DTYPE;
+    return launch_status();
+}
+
+CJ_EXPORT int cj_short_conv_commit(const float* in, int ld_in, int C, int taps, float* state, long long slot_stride,
+                                   const int* req_start, const int* req_slot, int requests, cudaStream_t stream) {
+    if (requests <= 0 || taps <= 1) return 0;
+    if (!in || !state || !req_start || !req_slot || C <= 0) return CJ_ERR_ARG;
+    int threads = C >= 512 ? 256 : 128;
+    int by = (C + threads - 1) / threads;
+    if (by > 64) by = 64;
+    cj::launch(short_conv_commit_kernel, dim3(requests, by), dim3(threads), 0, stream, in, ld_in, C, taps, state, slot_stride, req_start, req_slot);
+    return launch_status();
+}
+
+// mode 0: the state-space scan (off_a = B, off_b = C, off_v = x; off_dt in raw);
+// mode 1: the gated delta rule (off_a = q, off_b = k, off_v = v; off_dt = decay input, off_beta in raw).
+CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off_b, int off_v, const float* raw, int ld_raw,
+                            int off_dt, int off_beta, const float* A_log, const float* dt_bias, const float* skip, float* state,
+                            long long slot_stride, const int* req_start, const int* req_slot, float* out, int requests,
+                            int heads, int groups, int rows, int cols, float q_scale, cudaStream_t stream) {
+    if (requests <= 0) return 0;
+    if (!x || !raw || !A_log || !dt_bias || !state || !req_start || !req_slot || !out) return CJ_ERR_ARG;
+    if (mode == 0 && !skip) return CJ_ERR_ARG;
+    if (heads <= 0 || groups <= 0 || heads % groups != 0 || rows <= 0 || cols <= 0) return CJ_ERR_SIZE;
+    // a column's rows are dealt to DP lanes with at most 64 rows each
+    int DP = 4;
+    while (DP < 32 && (rows + DP - 1) / DP > 64) DP <<= 1;
+    const int per = (rows + DP - 1) / DP;
+    if (per > 64) return CJ_ERR_SIZE;
+    ScanArgs p{x, ld, off_a, off_b, off_v, raw, ld_raw, off_dt, off_beta, A_log, dt_bias, skip, state, slot_stride,
+               req_start, req_slot, out, heads, groups, rows, cols, q_scale};
+    const int cols_per_block = 4 * (32 / DP);
+    dim3 grid(requests, heads, (cols + cols_per_block - 1) / cols_per_block);
+    if (grid.y > 65535 || grid.z > 65535) return CJ_ERR_SIZE;
+#define LAUNCH(N)                                                                                   \
+    do {                                                                                            \
+        if (mode == 0) cj::launch(scan_kernel<N, false>, grid, dim3(128), 0, stream, p, DP);        \
+        else cj::launch(scan_kernel<N, true>, grid, dim3(128), 0, stream, p, DP);                   \
+    } while (0)
+    if (per <= 8) LAUNCH(8);
+    else if (per <= 16) LAUNCH(16);
+    else if (per <= 32) LAUNCH(32);
+    else LAUNCH(64);
+#undef LAUNCH
+    return launch_status();
+}
+
+CJ_EXPORT int cj_gated_group_norm(const float* y, int n, int part_len, const float* z, int ld_z, const float* w, int w_len,
+                                  float eps, int gate_first, void* out, int out_dtype, int rows, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!y || !z || !w || !out || n <= 0 || part_len <= 0 || w_len <= 0) return CJ_ERR_ARG;
+    if (n % part_len != 0) return CJ_ERR_SIZE;
+    const int parts = n / part_len;
+    int warps = parts < 8 ? parts : 8;
+    int by = (parts + warps - 1) / warps;
+    if (by > 64) by = 64;
+    dim3 grid(rows, by);
+    if (out_dtype == CJ_F32) cj::launch(gated_group_norm_kernel<float>, grid, dim3(warps * 32), 0, stream, y, n, part_len, z, ld_z, w, w_len, eps, gate_first, (float*)out);
+    else if (out_dtype == CJ_BF16) cj::launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(warps * 32), 0, stream, y, n, part_len, z, ld_z, w, w_len, eps, gate_first, (__nv_bfloat16*)out);
+    else return CJ_ERR_DTYPE;
+    return launch_status();
+}

@@ -98,11 +98,13 @@ class Runtime:
 @dataclass(frozen=True)
 class KvNeed:
     """A mixer that caches keys and values: pages of ``kv_heads x head_dim`` per token;
-    ``window`` > 0 means only the last ``window`` positions are ever read."""
+    ``window`` > 0 means only the last ``window`` positions are ever read.  ``values`` false:
+    one vector per token is all it caches (no plane of values is kept)."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -122,6 +124,9 @@ class Part:
         self.runtime = runtime
 
     def name(self, suffix: str) -> str:
+        """Tensor name under this part's prefix; an empty suffix names the prefix itself."""
+        if not suffix:
+            return self.prefix
         return f"{self.prefix}.{suffix}" if self.prefix else suffix
 
     def params(self) -> Dict[str, ParamSpec]:

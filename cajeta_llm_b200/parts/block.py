@@ -5,6 +5,13 @@ residual stream ``hs`` in float32 (model/DecoderLayer.cajeta:38-75,
 model/CausalLM.cajeta:1445-1446,1506,1512-1517,1575).  Parameters: the tensor-name
 pieces ``mixer_norm_name``, ``feed_forward_norm_name``, ``mixer_name``,
 ``feed_forward_name`` under the layer's prefix.
+
+``outnorm``: the norm sits on each sublayer's OUTPUT and the sublayers read the stream
+itself: ``hs += norm_1(mixer(hs)); hs += norm_2(feed_forward(hs))``.  A layer may have no
+feed-forward (``LayerSpec.feed_forward`` is None).  The sublayers see ``hs`` rounded to
+the activation dtype (a feed-forward that wants its input exactly gets the float32 stream
+itself); each adds its result into a zeroed float32 buffer of the stream's shape, which one
+kernel norms and adds.  Same parameters as ``prenorm``.
 """
 from __future__ import annotations
 
@@ -12,6 +19,7 @@ from typing import Dict
 
 import torch
 
+from ..csrc import kernels as K
 from .base import Part, make_part, register_part
 from .plan import LayerSpec, ParamSpec
 
@@ -57,3 +65,64 @@ class PreNormBlock(Part):
         x, x_exact = self.feed_forward_norm.forward(hs, want_f32=getattr(ff, "needs_f32_input", False) and not split,
                                                     pending=pending, want_split=split)
         ff.forward(x, x_exact, hs, ctx)
+
+
+@register_part("block", "outnorm")
+class OutputNormBlock(Part):
+    def __init__(self, spec, prefix, runtime, layer: LayerSpec):
+        super().__init__(spec, prefix, runtime)
+        self.mixer_norm = make_part("norm", layer.mixer_norm, self.name(spec["mixer_norm_name"]), runtime)
+        self.mixer = make_part("mixer", layer.mixer, self.name(spec["mixer_name"]), runtime)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = make_part("norm", layer.feed_forward_norm, self.name(spec["feed_forward_norm_name"]), runtime)
+            self.feed_forward = make_part("feed_forward", layer.feed_forward, self.name(spec["feed_forward_name"]), runtime)
+        for n in (self.mixer_norm, self.feed_forward_norm):
+            if n is not None and not (hasattr(n, "weight") and hasattr(n, "eps")):
+                raise ValueError("an outnorm block takes norms that are a weight and an eps (rmsnorm)")
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None)
+
+    def params(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for p in self.parts():
+            out.update(p.params())
+        return out
+
+    def libraries(self) -> set:
+        out = {"recurrent"}
+        for p in self.parts():
+            out |= p.libraries()
+        return out
+
+    def load(self, source) -> None:
+        for p in self.parts():
+            p.load(source)
+
+    def _input(self, hs: torch.Tensor) -> torch.Tensor:
+        rt = self.runtime
+        if rt.act_dtype == torch.float32:
+            return hs
+        x = torch.empty(hs.shape, dtype=rt.act_dtype, device=hs.device)
+        K.tag = "cast"
+        K.cast_rows(hs, x)
+        return x
+
+    def _add_normed(self, hs: torch.Tensor, y: torch.Tensor, pending, norm) -> None:
+        if pending is not None:
+            y += pending.sum(dim=0)
+        K.tag = "norm + add"
+        K.rmsnorm_add(hs, y, norm.weight, norm.eps)
+        K.tag = None
+
+    def forward(self, hs: torch.Tensor, ctx, entry) -> None:
+        y = torch.zeros_like(hs)
+        pending = self.mixer.forward(self._input(hs), y, ctx, entry)
+        self._add_normed(hs, y, pending, self.mixer_norm)
+        ff = self.feed_forward
+        if ff is None:
+            return
+        y = torch.zeros_like(hs)
+        ff.forward(self._input(hs), hs if getattr(ff, "needs_f32_input", False) else None, y, ctx)
+        self._add_normed(hs, y, None, self.feed_forward_norm)

@@ -2,7 +2,8 @@
 
 ``dense_swiglu``: ``W_d (silu(W_g x) * (W_u x))``, ``silu(x) = x / (1 + exp(-x))``
 (model/Prim.cajeta:1822-1847, model/CausalLM.cajeta:1556-1566).  Parameters:
-``hidden_size``, ``intermediate_size``.
+``hidden_size``, ``intermediate_size``, ``names`` (optional: the tensor names of
+``gate``, ``up`` and ``down`` under the part's prefix).
 
 ``sparse_moe``: router logits ``l_e = Wr[e] . x`` in float32, softmax over all experts,
 top-k by repeated strict-``>`` argmax (ties to the lower index), weights = the picked
@@ -18,7 +19,13 @@ width which ride through the same two grouped products as extra groups that ever
 belongs to (their partial down-projections are summed in chunk order by the combine):
 one launch streams all expert weights of the layer.
 Parameters: ``hidden_size``, ``num_experts``, ``top_k``, ``expert_intermediate_size``,
-``shared_intermediate_size`` (0 = none), ``shared_gate``, ``norm_topk_prob``.
+``shared_intermediate_size`` (0 = none), ``shared_gate``, ``norm_topk_prob``;
+``score`` (``softmax`` over all experts, the default, or ``sigmoid``: each expert's own
+sigma(l_e); the order of the experts is the same, the weights differ); ``weight_on``
+(``output``, the default: y = sum_j w_j expert_j(x); or ``input``: y = sum_j expert_j(w_j x),
+the weight multiplying the float32 row before it is rounded for the products);
+``names`` (optional tensor-name templates under the part's prefix: ``router``, and
+``gate`` / ``up`` / ``down`` with ``{e}`` for the expert's index).
 
 The file stores one tensor per expert and projection
 (``experts.{e}.gate_proj.weight`` ...); they are stacked into ``[E, I, H]`` and
@@ -45,13 +52,17 @@ class DenseSwiGLU(Part):
         super().__init__(spec, prefix, runtime)
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
+        names = dict(spec.get("names") or {})
+        self.n_gate = self.name(names.get("gate", "gate_proj.weight"))
+        self.n_up = self.name(names.get("up", "up_proj.weight"))
+        self.n_down = self.name(names.get("down", "down_proj.weight"))
         self.w_gate = self.w_up = self.w_down = None
 
     def params(self) -> Dict[str, ParamSpec]:
         return {
-            self.name("gate_proj.weight"): ParamSpec((self.inter, self.hidden)),
-            self.name("up_proj.weight"): ParamSpec((self.inter, self.hidden)),
-            self.name("down_proj.weight"): ParamSpec((self.hidden, self.inter)),
+            self.n_gate: ParamSpec((self.inter, self.hidden)),
+            self.n_up: ParamSpec((self.inter, self.hidden)),
+            self.n_down: ParamSpec((self.hidden, self.inter)),
         }
 
     def libraries(self) -> set:
@@ -61,9 +72,9 @@ class DenseSwiGLU(Part):
         return libs
 
     def load(self, source) -> None:
-        self.w_gate = self.fetch(source, self.name("gate_proj.weight"))
-        self.w_up = self.fetch(source, self.name("up_proj.weight"))
-        self.w_down = self.fetch(source, self.name("down_proj.weight"))
+        self.w_gate = self.fetch(source, self.n_gate)
+        self.w_up = self.fetch(source, self.n_up)
+        self.w_down = self.fetch(source, self.n_down)
 
     def forward(self, x: torch.Tensor, x_f32: Optional[torch.Tensor], residual: torch.Tensor, ctx) -> None:
         T = x.shape[0]
@@ -88,6 +99,15 @@ class SparseMoE(Part):
         self.shared_inter = int(spec.get("shared_intermediate_size", 0) or 0)
         self.shared_gate = bool(spec.get("shared_gate", False)) and self.shared_inter > 0
         self.norm_topk = bool(spec.get("norm_topk_prob", False))
+        self.score = str(spec.get("score", "softmax"))
+        self.weight_on = str(spec.get("weight_on", "output"))
+        if self.score not in ("softmax", "sigmoid"):
+            raise ValueError(f"score must be 'softmax' or 'sigmoid', found '{self.score}'")
+        if self.weight_on not in ("output", "input"):
+            raise ValueError(f"weight_on must be 'output' or 'input', found '{self.weight_on}'")
+        names = dict(spec.get("names") or {})
+        self.n_router = self.name(names.get("router", "gate.weight"))
+        self.n_expert = {proj: names.get(proj, f"experts.{{e}}.{proj}_proj.weight") for proj in ("gate", "up", "down")}
         if not 1 <= self.top_k <= self.num_experts:
             raise ValueError(f"top_k must be between 1 and num_experts ({self.num_experts}), found {self.top_k}")
         if self.num_experts > 1024:
@@ -103,11 +123,11 @@ class SparseMoE(Part):
             self.shared_chunks = self.shared_inter // self.inter
 
     def params(self) -> Dict[str, ParamSpec]:
-        p = {self.name("gate.weight"): ParamSpec((self.num_experts, self.hidden), role="vector")}
+        p = {self.n_router: ParamSpec((self.num_experts, self.hidden), role="vector")}
         for e in range(self.num_experts):
-            p[self.name(f"experts.{e}.gate_proj.weight")] = ParamSpec((self.inter, self.hidden))
-            p[self.name(f"experts.{e}.up_proj.weight")] = ParamSpec((self.inter, self.hidden))
-            p[self.name(f"experts.{e}.down_proj.weight")] = ParamSpec((self.hidden, self.inter))
+            p[self.expert_name("gate", e)] = ParamSpec((self.inter, self.hidden))
+            p[self.expert_name("up", e)] = ParamSpec((self.inter, self.hidden))
+            p[self.expert_name("down", e)] = ParamSpec((self.hidden, self.inter))
         if self.shared_inter > 0:
             p[self.name("shared_expert.gate_proj.weight")] = ParamSpec((self.shared_inter, self.hidden))
             p[self.name("shared_expert.up_proj.weight")] = ParamSpec((self.shared_inter, self.hidden))
@@ -116,27 +136,30 @@ class SparseMoE(Part):
                 p[self.name("shared_expert_gate.weight")] = ParamSpec((1, self.hidden), role="vector")
         return p
 
+    def expert_name(self, proj: str, e: int) -> str:
+        return self.name(self.n_expert[proj].format(e=e))
+
     def libraries(self) -> set:
-        libs = {"rowwise", "moe_route", "gemm_simt"}
+        libs = {"rowwise", "moe_route", "gemm_simt"} | ({"recurrent"} if self.weight_on == "input" else set())
         if self.runtime.fast_kernels and self.hidden >= 128:
             libs |= {"gemm_tc", "gemm_tc2"}
         return libs
 
     def load(self, source) -> None:
         rt = self.runtime
-        self.router = self.fetch(source, self.name("gate.weight"))
+        self.router = self.fetch(source, self.n_router)
 
         E, C, I = self.num_experts, self.shared_chunks, self.inter
 
         def slab(proj: str, rows: int, cols: int) -> torch.Tensor:
             out = torch.empty((E + C, rows, cols), dtype=rt.matrix_dtype, device=rt.device)
             for e in range(E):
-                out[e].copy_(self.fetch(source, self.name(f"experts.{e}.{proj}.weight")))
+                out[e].copy_(self.fetch(source, self.expert_name(proj, e)))
             return out
 
-        self.w_gate = slab("gate_proj", I, self.hidden)
-        self.w_up = slab("up_proj", I, self.hidden)
-        self.w_down = slab("down_proj", self.hidden, I)
+        self.w_gate = slab("gate", I, self.hidden)
+        self.w_up = slab("up", I, self.hidden)
+        self.w_down = slab("down", self.hidden, I)
         if self.shared_inter > 0:
             ws_gate = self.fetch(source, self.name("shared_expert.gate_proj.weight"))
             ws_up = self.fetch(source, self.name("shared_expert.up_proj.weight"))
@@ -190,7 +213,8 @@ class SparseMoE(Part):
     SHARED_DENSE_MIN_ROWS = 512
 
     def wants_split_input(self, rows: int) -> bool:
-        return self.router_split is not None and rows >= self.SPLIT_ROUTER_MIN_ROWS
+        # with the weight on the expert's input the float32 row itself is needed, not its three-term form
+        return self.router_split is not None and rows >= self.SPLIT_ROUTER_MIN_ROWS and self.weight_on == "output"
 
     def _route(self, x_exact: torch.Tensor, sel, wts, shared_scale, pin=None, gap=None) -> None:
         k = self.top_k
@@ -206,9 +230,11 @@ class SparseMoE(Part):
             logits = torch.empty((splits, T, cols), dtype=torch.float32, device=x_exact.device)
             K.gemm_tc(x_exact, self.router_split, logits if splits > 1 else logits[0], K.EPI_STORE_F32, False, 128,
                       k_splits=splits)
-            K.router_select(logits, self.num_experts, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap)
+            K.router_select(logits, self.num_experts, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap,
+                            sigmoid_scores=self.score == "sigmoid")
         else:
-            K.router_topk(x_exact, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap)
+            K.router_topk(x_exact, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap,
+                          sigmoid_scores=self.score == "sigmoid")
 
     def forward(self, x: torch.Tensor, x_exact: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         rt = self.runtime
@@ -240,9 +266,22 @@ class SparseMoE(Part):
 
         act = torch.empty((n_slots, self.inter), dtype=rt.act_dtype, device=dev)
         G = E + C
-        K.tag = "experts gate/up"
-        project(rt, x, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, a_row_index=slot_token,
-                max_group_rows=T)
+        if self.weight_on == "input":
+            # a pick's score multiplies the float32 row; the product then reads the scaled rows in
+            # the grouped order, and the combine adds the experts' results unweighted
+            if C > 0 or self.shared_inter > 0:
+                raise ValueError("weight_on='input' with a shared expert is not built")
+            scaled = torch.empty((n_slots, self.hidden), dtype=rt.act_dtype, device=dev)
+            K.tag = "row gather"
+            K.scale_rows_gather(x_exact, slot_of_pick, wts, k, scaled)
+            K.tag = "experts gate/up"
+            project(rt, scaled, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, max_group_rows=T,
+                    offsets_settled=True)
+            wts = torch.ones_like(wts)
+        else:
+            K.tag = "experts gate/up"
+            project(rt, x, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, a_row_index=slot_token,
+                    max_group_rows=T)
         y = torch.empty((n_slots, self.hidden), dtype=torch.float32, device=dev)
         K.tag = "experts down"
         project(rt, act, self.w_down[:G], y, group_offsets=offsets, max_group_rows=T, offsets_settled=True)

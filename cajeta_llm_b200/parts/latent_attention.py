@@ -1,0 +1,135 @@
+"""Attention over a compressed latent (one cache entry per token, shared by all heads).
+
+Per row at position p, H heads with ``dim`` unrotated and ``rot_dim`` rotated query/key
+entries, values of ``vdim``, latent of ``kv_rank``::
+
+    q = W_q x                       laid out head by head as [dim | rot_dim]
+    d = W_dkv x                     kv_rank + rot_dim rows
+    c = rms(d[:kv_rank]) * w        the latent           } one cache entry
+    r = rotate(d[kv_rank:], p)      the shared key part  } of kv_rank + rot_dim
+    k_h = [W_uk[h] c | r] ,  v_h = W_uv[h] c
+    score_h,j = (q_h[:dim] . W_uk[h] c_j + rotate(q_h[dim:], p) . r_j) * scale ,  j <= p
+    out_h = sigmoid(W_g x)_h * sum_j softmax(score_h)_j v_h,j ;  then W_o on the heads
+
+The rotation pairs entries (2i, 2i+1) of the first ``rotary_dim`` entries of the rotated
+part (the position part's ``rotary_dim`` and ``inv_freq``).  Nothing per head is built from
+the cache: ``W_uk[h]^T q`` is taken on the query's side and ``W_uv[h]`` applied to the
+weighted sum of latents, so the attention kernel reads each cache entry once for all
+heads.  An entry that reads another entry's cache (``entry.writes_cache`` false) has no
+``W_dkv`` of its own: it attends over that entry's latents and key parts with its own
+queries, ``W_uk`` and ``W_uv``.
+
+Parameters: ``hidden_size``, ``heads``, ``dim``, ``rot_dim``, ``vdim``, ``kv_rank``,
+``scale``, ``eps``, ``position`` (a position PartSpec), ``owns_cache`` (false: no ``dkv``
+tensors).  Tensors: ``q``, ``g``, ``dkv``, ``dkv.norm``, ``uk``, ``uv``, ``o``.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import kernels as K
+from .base import KvNeed, Part, make_part, register_part
+from .linear import project
+from .plan import ParamSpec
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Part):
+    def __init__(self, spec, prefix, runtime):
+        super().__init__(spec, prefix, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.heads = int(spec["heads"])
+        self.dim = int(spec["dim"])
+        self.rot = int(spec["rot_dim"])
+        self.vdim = int(spec["vdim"])
+        self.rank = int(spec["kv_rank"])
+        self.scale = float(spec["scale"])
+        self.eps = float(spec["eps"])
+        self.owns_cache = bool(spec.get("owns_cache", True))
+        self.position = make_part("position", spec["position"], prefix, runtime)
+        self.rotary = int(self.position.rotary_dim)
+        if self.rotary > self.rot:
+            raise ValueError(f"the position part rotates {self.rotary} entries; the rotated part has {self.rot}")
+        if self.rank > 1024:
+            raise ValueError(f"kv_rank {self.rank} is larger than the attention kernel takes (1024)")
+        self.nq = self.heads * (self.dim + self.rot)
+        self.w_in = self.w_norm = self.w_uk_t = self.w_uv = self.w_o = None
+
+    def cache_need(self) -> Optional[KvNeed]:
+        return KvNeed(1, self.rank + self.rot, 0, values=False)
+
+    def state_need(self):
+        return None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p = {
+            self.name("q"): ParamSpec((self.nq, self.hidden)),
+            self.name("g"): ParamSpec((self.heads, self.hidden)),
+            self.name("uk"): ParamSpec((self.heads * self.dim, self.rank)),
+            self.name("uv"): ParamSpec((self.heads * self.vdim, self.rank)),
+            self.name("o"): ParamSpec((self.hidden, self.heads * self.vdim)),
+        }
+        if self.owns_cache:
+            p[self.name("dkv")] = ParamSpec((self.rank + self.rot, self.hidden))
+            p[self.name("dkv.norm")] = ParamSpec((self.rank,), role="vector", init="ones")
+        return p
+
+    def libraries(self) -> set:
+        libs = {"latent_attention", "gemm_simt"}
+        if self.runtime.fast_kernels and self.hidden >= 128:
+            libs |= {"gemm_tc", "gemm_tc2"}
+        return libs
+
+    def load(self, source) -> None:
+        rows = [self.fetch(source, self.name("q")), self.fetch(source, self.name("g"))]
+        if self.owns_cache:
+            rows.append(self.fetch(source, self.name("dkv")))
+            self.w_norm = self.fetch(source, self.name("dkv.norm"))
+        self.w_in = torch.cat(rows, dim=0).contiguous()              # q | g | dkv: one product
+        uk = self.fetch(source, self.name("uk"))
+        # head h's W_uk^T as the weight of a product over dim: [heads, kv_rank, dim]
+        self.w_uk_t = uk.view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = self.fetch(source, self.name("uv")).view(self.heads, self.vdim, self.rank).contiguous()
+        self.w_o = self.fetch(source, self.name("o"))
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> None:
+        rt = self.runtime
+        dev = x.device
+        T, H = x.shape[0], self.heads
+        write = entry.writes_cache
+        if write and not self.owns_cache:
+            raise ValueError(f"{self.prefix}: the plan lets this entry write a cache, but the part has no W_dkv")
+        n_out = self.nq + H + ((self.rank + self.rot) if write else 0)
+        proj = torch.empty((T, n_out), dtype=torch.float32, device=dev)
+        K.tag = "mixer in"
+        project(rt, x, self.w_in[:n_out], proj)
+        inv_freq = self.position.inv_freq
+        if write:
+            K.tag = "latent norm + rope + cache write"
+            K.latent_kv_write(proj, self.nq + H, self.rank, self.rot, self.rotary, self.w_norm, self.eps, inv_freq,
+                              ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens, entry.k_plane)
+        q_plain = torch.empty((H * T, self.dim), dtype=rt.act_dtype, device=dev)
+        q_rot = torch.empty((T, H, self.rot), dtype=torch.float32, device=dev)
+        K.tag = "q split + rope"
+        K.latent_q_split(proj, H, self.dim, self.rot, self.rotary, inv_freq, ctx.positions, q_plain, q_rot)
+        # rows are head-major: group h of the grouped products is head h's T rows
+        offsets = torch.arange(0, (H + 1) * T, T, dtype=torch.int32, device=dev)
+        q_abs = torch.empty((H * T, self.rank), dtype=torch.float32, device=dev)
+        K.tag = "q absorb"
+        project(rt, q_plain, self.w_uk_t, q_abs, group_offsets=offsets, max_group_rows=T)
+        lat = torch.empty((H * T, self.rank), dtype=rt.cache_dtype, device=dev)
+        K.tag = "attention"
+        K.latent_attention(q_abs, q_rot, entry.k_plane, self.rank, self.rot, H, ctx.positions, ctx.row_req, entry.block_table,
+                           entry.page_tokens, self.scale, lat)
+        o = torch.empty((H * T, self.vdim), dtype=torch.float32, device=dev)
+        K.tag = "value up"
+        project(rt, lat, self.w_uv, o, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
+        gated = torch.empty((T, H * self.vdim), dtype=rt.act_dtype, device=dev)
+        K.tag = "head gate"
+        K.latent_gate_out(o, proj, self.nq, H, self.vdim, gated)
+        K.tag = "o"
+        project(rt, gated, self.w_o, residual, accumulate=True)
+        K.tag = None
+        return None

@@ -2,7 +2,8 @@
 
 ``ss = sum x_i^2; scale = 1 / sqrt(ss / dim + eps); y_i = x_i * scale * w_i`` with the
 statistics in float32 (model/Prim.cajeta:120-151; weight and eps held per norm,
-model/RMSNorm.cajeta:14-53).  Parameters: ``dim``, ``eps``.
+model/RMSNorm.cajeta:14-53).  Parameters: ``dim``, ``eps``, ``weight_name`` (the weight's
+tensor name under the part's prefix, default ``weight``; empty: the prefix itself).
 """
 from __future__ import annotations
 
@@ -21,16 +22,17 @@ class RMSNorm(Part):
         super().__init__(spec, prefix, runtime)
         self.dim = int(spec["dim"])
         self.eps = float(spec["eps"])
+        self.weight_name = self.name(spec.get("weight_name", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {self.name("weight"): ParamSpec((self.dim,), role="vector", init="ones")}
+        return {self.weight_name: ParamSpec((self.dim,), role="vector", init="ones")}
 
     def libraries(self) -> set:
         return {"rowwise"}
 
     def load(self, source) -> None:
-        self.weight = self.fetch(source, self.name("weight"))
+        self.weight = self.fetch(source, self.weight_name)
 
     def forward(self, x: torch.Tensor, want_f32: bool = False, row_index: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None, pending: Optional[torch.Tensor] = None,

@@ -68,9 +68,9 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]          # None: the layer has no feed-forward (a block kind must allow it)
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
 
 
 @dataclass(frozen=True)
