@@ -197,3 +197,43 @@ def forward(tokens, weights, config, positions=None):
         after.append(x.clone())
     logits = (rms_unit(x, eps) * weights["final.norm"]) @ weights["head"].T
     return logits, torch.stack(after)
+
+
+# -- reading a model folder (a reader of its own: 8-byte length, JSON header, raw data) -------
+def read_model(model_dir):
+    import json
+    import os
+    import struct
+
+    import numpy as np
+
+    with open(os.path.join(model_dir, "config.json")) as f:
+        config = json.load(f)
+    with open(os.path.join(model_dir, "model.safetensors"), "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        data = f.read()
+    weights = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = info["data_offsets"]
+        raw = data[lo:hi]
+        if info["dtype"] == "BF16":
+            bits = np.frombuffer(raw, dtype=np.uint16).astype(np.uint32) << 16
+            t = torch.from_numpy(bits.view(np.float32).copy()).to(F64)
+        elif info["dtype"] == "F32":
+            t = torch.from_numpy(np.frombuffer(raw, dtype=np.float32).copy()).to(F64)
+        else:
+            raise ValueError(f"{name}: dtype {info['dtype']}")
+        weights[name] = t.reshape(info["shape"])
+    return config, weights
+
+
+def greedy(config, weights, prompt, n):
+    toks, out = list(prompt), []
+    for _ in range(n):
+        logits, _ = forward(toks, weights, config)
+        out.append(int(torch.argmax(logits[-1])))
+        toks.append(out[-1])
+    return out

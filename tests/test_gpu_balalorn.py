@@ -1,0 +1,305 @@
+"""Balalorn through the engine against the plain implementation (``plain_balalorn.py``).
+
+Small configurations of their own (sizes that differ in every field; groups, key heads,
+norm parts and picked experts that are neither 1 nor equal to one another; a rotation over
+fewer entries than the rotated part has; a layer without feed-forward; a layer that reads
+the latent cache of a layer two before it).  Each mixer and feed-forward alone as a
+one-layer model; whole prompts against token-by-token decoding and against portions down to
+two tokens; unequal requests in one batch against each alone; slots and pages used again;
+far keys and page borders with attention made sharp; first tokens; long decoding; greedy
+generation through the entry point and its scheduler.
+"""
+import copy
+import json
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_balalorn as P
+
+pytestmark = pytest.mark.gpu
+
+LATENT = {"type": "latent_attention",
+          "mixer": {"heads": 3, "dim": 16, "rot_dim": 8, "vdim": 12, "kv_rank": 20, "scale": 0.21,
+                    "rot": {"base": 10000.0, "dims": 4}},
+          "mlp": None}
+LATENT_SHARED = {"type": "latent_attention",
+                 "mixer": {"heads": 2, "dim": 8, "rot_dim": 8, "vdim": 16, "kv_rank": 20, "scale": 0.3, "kv_from": 0,
+                           "rot": {"base": 10000.0, "dims": 4}},
+                 "mlp": {"kind": "dense", "ff": 40}}
+SSD = {"type": "mamba2", "mixer": {"heads": 6, "vdim": 8, "state": 12, "groups": 3, "norm_groups": 1, "conv": 2}, "mlp": None}
+SSD_B = {"type": "mamba2", "mixer": {"heads": 4, "vdim": 20, "state": 9, "groups": 1, "norm_groups": 5, "conv": 5},
+         "mlp": {"kind": "moe", "expert": {"ff": 24}, "router": {"experts": 5, "top": 2}}}
+DELTA = {"type": "delta", "mixer": {"heads": 6, "kv_heads": 2, "dim": 12, "vdim": 10, "conv": 5},
+         "mlp": {"kind": "moe", "expert": {"ff": 16}, "router": {"experts": 4, "top": 3}}}
+DELTA_B = {"type": "delta", "mixer": {"heads": 2, "kv_heads": 2, "dim": 40, "vdim": 7, "conv": 2}, "mlp": {"kind": "dense", "ff": 48}}
+
+
+def config_of(layers, width=64, vocab=200, eps=1e-5):
+    return {"architecture": "Balalorn", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": copy.deepcopy(layers)}
+
+
+CONFIGS = {
+    "mixed": config_of([LATENT, SSD, LATENT_SHARED, DELTA, DELTA_B]),
+    "other": config_of([DELTA_B, SSD_B, LATENT, dict(LATENT_SHARED, mixer=dict(LATENT_SHARED["mixer"], kv_from=2))], width=72, vocab=150, eps=1e-6),
+    # wide enough for the tensor-core products of the bfloat16 path
+    "wide": config_of([
+        {"type": "latent_attention", "mixer": {"heads": 4, "dim": 128, "rot_dim": 16, "vdim": 128, "kv_rank": 128, "scale": 0.08,
+                                                "rot": {"base": 50000.0, "dims": 16}},
+         "mlp": {"kind": "moe", "expert": {"ff": 128}, "router": {"experts": 6, "top": 2}}},
+        {"type": "mamba2", "mixer": {"heads": 8, "vdim": 32, "state": 16, "groups": 2, "norm_groups": 2, "conv": 4},
+         "mlp": {"kind": "dense", "ff": 256}},
+        {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 3}, "mlp": {"kind": "dense", "ff": 256}},
+    ], width=256, vocab=500),
+}
+ALONE = {"latent": [LATENT], "latent+shared": [LATENT, LATENT_SHARED], "ssd": [SSD], "ssd_b": [SSD_B], "delta": [DELTA],
+         "delta_b": [DELTA_B]}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    made = {}
+
+    def get(name, raw, seed=5, touch=None):
+        if name not in made:
+            d = str(tmp_path_factory.mktemp(f"balalorn_{name.replace('+', '_')}"))
+            helpers.write_model(d, raw, seed=seed)
+            if touch is not None:
+                touch(d)
+            made[name] = (d, P.read_model(d))
+        return made[name]
+    return get
+
+
+def runner_for(model_dir, dtype, max_seqs=4, max_tokens=512, num_pages=None, cuda_graphs=True, page=16):
+    import cajeta_llm_b200  # noqa: F401
+    from cajeta_llm_b200.engine.model import load_model
+    from cajeta_llm_b200.engine.step import ModelRunner
+    from cajeta_llm_b200.parts.base import Runtime
+    model, _ = load_model(model_dir, Runtime(dtype, "cuda:0"))
+    return ModelRunner(model, page_tokens=page, max_seqs=max_seqs, max_tokens_per_seq=max_tokens,
+                       num_pages=num_pages if num_pages is not None else -(-max_tokens // page) * max_seqs, cuda_graphs=cuda_graphs)
+
+
+def feed(runner, slot, tokens, cuts):
+    """The request's tokens in steps of the given sizes; logits of every position."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    out, at = [], 0
+    for n in cuts:
+        out.append(runner.step([StepEntry(slot, tokens[at:at + n], list(range(n)))]).cpu())
+        at += n
+    assert at == len(tokens)
+    return torch.cat(out)
+
+
+def rel_err(got, want):
+    """Per row: RMS of the difference (mean taken off) over the RMS of the wanted logits."""
+    d = got.double() - want.double()
+    d = d - d.mean(dim=-1, keepdim=True)
+    w = want.double() - want.double().mean(dim=-1, keepdim=True)
+    return d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt().clamp_min(1e-9)
+
+
+def check(got, want, dtype, what):
+    e = rel_err(got, want)
+    if dtype == "float32":
+        assert float(e.max()) < 3e-5, f"{what}: worst row {int(e.argmax())} differs by {float(e.max()):.2e}"
+    else:
+        # bfloat16 storage of activations; a row whose last picked expert was nearly tied may swap it
+        assert float(e.median()) < 2e-2 and float((e > 6e-2).float().mean()) <= 0.04, \
+            f"{what}: median {float(e.median()):.3f}, worst {float(e.max()):.3f}, over 0.06: {int((e > 6e-2).sum())} of {e.numel()}"
+
+
+@pytest.mark.parametrize("name", sorted(ALONE))
+def test_each_mechanism_alone_as_a_one_layer_model(folders, name):
+    d, (cfg, W) = folders(name, config_of(ALONE[name], width=48, vocab=90), seed=3)
+    toks = helpers.random_tokens(90, 41, seed=1)
+    want, _ = P.forward(toks, W, cfg)
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_tokens=64)
+        s = r.admit()
+        check(feed(r, s, toks, [41]), want, dtype, f"{name} whole {dtype}")
+        r.release(s)
+        s = r.admit()                                  # the same slot again: its state starts at zero
+        check(feed(r, s, toks, [5, 2, 17, 2, 3] + [1] * 12), want, dtype, f"{name} portions {dtype}")
+
+
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_decoded_and_in_portions(folders, name, dtype):
+    d, (cfg, W) = folders(name, CONFIGS[name], seed=7)
+    toks = helpers.random_tokens(cfg["vocab"], 75, seed=2)
+    want, _ = P.forward(toks, W, cfg)
+    r = runner_for(d, dtype, max_tokens=128)
+    results = []
+    for cuts in ([75], [43] + [1] * 32, [1] * 75 if name != "wide" else [2] * 37 + [1], [7, 2, 16, 3, 2, 9, 5, 2, 15, 14]):
+        s = r.admit()
+        results.append(feed(r, s, toks, cuts))
+        check(results[-1], want, dtype, f"{name} {dtype} cuts {cuts[:4]}")
+        r.release(s)
+    if dtype == "float32":
+        # the cut changes nothing but the rounding of the products' sums
+        for other in results[1:]:
+            assert float(rel_err(other, results[0]).max()) < 1e-5
+
+
+def test_unequal_requests_in_one_batch_slots_and_pages_used_again(folders):
+    """Up to four live requests, portions of some beside single tokens of others, requests
+    that sit a step out, in a pool so small that pages and slots come back into use: every
+    position equals the plain implementation's, and in float32 the request run alone."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    d, (cfg, W) = folders("mixed", CONFIGS["mixed"], seed=7)
+    rng = random.Random(4)
+    lens = [23, 48, 17, 64, 35, 29, 52, 2, 41, 1]
+    toks = {i: helpers.random_tokens(cfg["vocab"], n, seed=50 + i) for i, n in enumerate(lens)}
+    want = {i: P.forward(t, W, cfg)[0] for i, t in toks.items()}
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_seqs=4, max_tokens=64, num_pages=14)
+        waiting, live, got = list(toks), {}, {i: [] for i in toks}
+        while waiting or live:
+            while waiting and len(live) < 4:
+                i = waiting[0]
+                if sum(-(-(len(toks[j]) + 15) // 16) for j in live) + -(-(len(toks[i]) + 15) // 16) > 14:
+                    break
+                waiting.pop(0)
+                live[i] = [r.admit(), 0, max(1, len(toks[i]) - rng.randint(3, 12))]
+            entries, who = [], []
+            for i, st in list(live.items()):
+                if len(live) > 1 and rng.random() < 0.2:
+                    continue
+                n = 1 if st[1] >= st[2] else min(rng.randint(2, 11), st[2] - st[1])
+                entries.append(StepEntry(st[0], toks[i][st[1]:st[1] + n], list(range(n))))
+                who.append((i, n))
+                st[1] += n
+            if not entries:
+                continue
+            out = r.step(entries).cpu()
+            at = 0
+            for i, n in who:
+                got[i].append(out[at:at + n])
+                at += n
+                if live[i][1] == len(toks[i]):
+                    r.release(live.pop(i)[0])
+        for i in toks:
+            check(torch.cat(got[i]), want[i], dtype, f"request {i} in the mixed batch ({dtype})")
+        r.cache.books.check()
+
+
+def sharpen(scale):
+    def touch(model_dir):
+        path = os.path.join(model_dir, "config.json")
+        with open(path) as f:
+            c = json.load(f)
+        for layer in c["layers"]:
+            if layer["type"] == "latent_attention":
+                layer["mixer"]["scale"] = scale
+        with open(path, "w") as f:
+            json.dump(c, f)
+    return touch
+
+
+def test_far_keys_and_page_borders_with_sharp_attention(folders):
+    """With random weights a softmax over hundreds of keys is nearly flat and a lost key hides
+    in it.  Here the scores are multiplied up until a row's weight sits on a few keys anywhere
+    in its past - a missing or shifted key, a page's first or last entry, then shows in that
+    row's logits.  Prompt portions that end inside, on and just past page borders, then decoding."""
+    raw = config_of([LATENT, LATENT_SHARED], width=48, vocab=90)
+    d, (cfg, W) = folders("sharp", raw, seed=9, touch=sharpen(40.0))
+    assert cfg["layers"][0]["mixer"]["scale"] == 40.0
+    toks = helpers.random_tokens(90, 330, seed=8)
+    want, _ = P.forward(toks, W, cfg)
+    # the weights really are concentrated: the largest softmax weight of late rows is far from 1/t
+    c, kr = P.latent_keys(W["embed"][torch.tensor(toks)], P.sub(W, "l0.mix"), cfg["layers"][0]["mixer"], cfg["norm"]["eps"], range(330))
+    assert c.shape == (330, 20)
+    r = runner_for(d, "float32", max_tokens=336)
+    for cuts in ([330], [15, 1, 1, 15, 16, 17, 31, 33, 64, 63, 2, 40] + [1] * 32, [255, 2, 41] + [1] * 32):
+        s = r.admit()
+        e = rel_err(feed(r, s, toks, cuts), want)
+        assert float(e.max()) < 1e-4, f"cuts {cuts[:5]}: row {int(e.argmax())} differs by {float(e.max()):.2e}"
+        r.release(s)
+    # and a deliberately wrong oracle (the far half of the keys dropped) is told apart by this test's bound
+    m = cfg["layers"][0]["mixer"]
+    near, _ = P.latent_attention(W["embed"][torch.tensor(toks[200:])], P.sub(W, "l0.mix"), m, cfg["norm"]["eps"], range(200, 330))
+    full, _ = P.latent_attention(W["embed"][torch.tensor(toks)], P.sub(W, "l0.mix"), m, cfg["norm"]["eps"], range(330))
+    assert float(rel_err(near[-30:], full[-30:]).max()) > 1e-2
+
+
+def test_first_tokens_and_long_decoding(folders):
+    """Single-token requests, requests shorter than a convolution's taps, and 150 tokens decoded
+    one by one after a 3-token prompt (state carried 150 times, two graph buckets of decode)."""
+    d, (cfg, W) = folders("other", CONFIGS["other"], seed=7)
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_tokens=192)
+        for n in (1, 2, 3, 4, 6):
+            toks = helpers.random_tokens(cfg["vocab"], n, seed=20 + n)
+            s = r.admit()
+            check(feed(r, s, toks, [1] * n), P.forward(toks, W, cfg)[0], dtype, f"{n} first tokens one by one ({dtype})")
+            r.release(s)
+        toks = helpers.random_tokens(cfg["vocab"], 153, seed=33)
+        s = r.admit()
+        check(feed(r, s, toks, [3] + [1] * 150), P.forward(toks, W, cfg)[0], dtype, f"long decoding ({dtype})")
+        r.release(s)
+
+
+def test_captured_steps_equal_uncaptured_ones(folders):
+    """bfloat16 steps replayed from CUDA graphs (decode steps and step shapes that come again)
+    give the bits of steps launched kernel by kernel, state included."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    d, (cfg, W) = folders("wide", CONFIGS["wide"], seed=7)
+    toks = [helpers.random_tokens(cfg["vocab"], 60, seed=70 + i) for i in range(3)]
+    outs = []
+    for graphs in (True, False):
+        r = runner_for(d, "bfloat16", max_tokens=128, cuda_graphs=graphs)
+        slots = [r.admit() for _ in toks]
+        got = []
+        for lo, hi in ((0, 12), (12, 24), (24, 36)):                # the same shape three times: captured, then replayed
+            got.append(r.step([StepEntry(s, t[lo:hi], [hi - lo - 1]) for s, t in zip(slots, toks)]).cpu())
+        for i in range(36, 60):
+            got.append(r.step([StepEntry(s, [t[i]], [0]) for s, t in zip(slots, toks)]).cpu())
+        outs.append(torch.cat(got))
+        if graphs:
+            assert r.graph_replays > 0
+    assert torch.equal(outs[0], outs[1])
+
+
+def test_greedy_generation_through_the_entry_point_and_its_scheduler(folders):
+    from cajeta_llm_b200.engine.llm_engine import LlmEngine
+    from cajeta_llm_b200.engine.options import EngineOptions
+    from cajeta_llm_b200.sampling.params import SamplingParams
+    d, (cfg, W) = folders("mixed", CONFIGS["mixed"], seed=7)
+    prompts = [helpers.random_tokens(cfg["vocab"], n, seed=90 + n) for n in (5, 9, 17, 30, 3, 12)]
+    want = [P.greedy(cfg, W, p, 6) for p in prompts]
+    # more requests than slots, portions of at most 8 tokens under a budget of 24 a step
+    eng = LlmEngine.load(EngineOptions(model=d, dtype="float32", ctx=64, max_seqs=3, chunk=8, max_batch_tokens=24))
+    got = eng.generate(prompts, SamplingParams(max_new_tokens=6, stop_token_ids=()))
+    assert got == want
+    eng.close()
+    eng = LlmEngine.load(EngineOptions(model=d, dtype="bfloat16", ctx=64, max_seqs=4))
+    got = eng.generate(prompts, SamplingParams(max_new_tokens=6, stop_token_ids=()))
+    same = sum(g == w for g, w in zip(got, want))
+    assert same >= len(prompts) - 1, f"bfloat16 greedy tokens differ for {len(prompts) - same} prompts"
+    eng.close()
+
+
+def test_replay_tool_on_a_model_folder(folders, tmp_path):
+    d, (cfg, W) = folders("other", CONFIGS["other"], seed=7)
+    a, b = helpers.random_tokens(cfg["vocab"], 20, seed=1), helpers.random_tokens(cfg["vocab"], 9, seed=2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:11], "want": [10]}, {"id": "b", "tokens": b[:8], "want": []}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[8:], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[11:], "want": [0, 8]}], "end": ["a"]}]
+    import subprocess
+    import sys
+    cmd = [sys.executable, os.path.join(helpers.ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", str(tmp_path),
+           "--max-tokens", "128"]
+    proc = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    wa, wb = P.forward(a, W, cfg)[0], P.forward(b, W, cfg)[0]
+    got = {n: torch.from_numpy(np.fromfile(os.path.join(str(tmp_path), f"{n}.f32"), dtype="<f4").reshape(-1, cfg["vocab"])) for n in range(3)}
+    check(got[0], wa[10:11], "float32", "step 0")
+    check(got[1], wb[8:9], "float32", "step 1")
+    check(got[2], wa[[11, 19]], "float32", "step 2")
