@@ -162,7 +162,7 @@ def run(args, peaks) -> int:
                 r.step([StepEntry(sl, toks(PROMPT), []) for sl in held])
                 return held, [StepEntry(sl, toks(1), [0]) for sl in held]
 
-            line = {"design": design, "size": size, "sizes": s, "weights_gb": round(eng.model.weight_bytes() / 1e9, 2),
+            line = {"design": design, "size": size, "sizes": s, "weights_gb": round(eng.model().weight_bytes() / 1e9, 2),
                     "prefill_tokens": PREFILL, "prefill_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(PREFILL / prefill_ms * 1e3),
                     "decode_batch": BATCH, "decode_context": PROMPT, "decode_ms_per_step": round(decode_ms, 3),
                     "decode_tokens_per_s": round(BATCH / decode_ms * 1e3), "peaks": pk,

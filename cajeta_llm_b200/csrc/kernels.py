@@ -467,21 +467,41 @@ def latent_q_split(q: torch.Tensor, heads: int, dim: int, rot: int, rotary: int,
     _check(st, "latent_q_split")
 
 
+LATENT_SPLIT_MIN_KEYS = 128      # a stretch of a row's keys is at least this long
+LATENT_FILL_BLOCKS = 592         # blocks that fill the machine (four an SM); fewer: the rows' keys are cut into stretches
+
+
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tensor, rank: int, rot: int, heads: int,
                      positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int, scale: float,
-                     out: torch.Tensor) -> None:
+                     out: torch.Tensor, max_context: int = 0) -> None:
     """Every (row, head): softmax over the row's keys [0, position] of (q_abs . c + q_rot . r) * scale,
     and the weighted sum of the latents.  q_abs float32 [heads, T, rank]; q_rot float32 [T, heads, rot];
-    out [heads, T, rank] in the cache's dtype."""
+    out [heads, T, rank] in the cache's dtype.  ``max_context`` (the longest row's keys, when the
+    caller knows it): with few rows the keys of a row are cut into stretches that run side by side."""
     _need(q_abs, "q_abs", torch.float32), _need(q_rot, "q_rot", torch.float32), _need(plane, "plane"), _need(out, "out", plane.dtype)
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     T = positions.numel()
     if q_abs.numel() != heads * T * rank or out.numel() != heads * T * rank or plane.shape[-1] != rank + rot:
         raise KernelError("latent_attention: sizes do not agree")
+    blocks = T * -(-heads // 8)
+    split_keys, splits, part_acc, part_ml = 0, 1, None, None
+    if max_context > LATENT_SPLIT_MIN_KEYS and blocks < LATENT_FILL_BLOCKS:
+        want = -(-LATENT_FILL_BLOCKS // blocks)
+        split_keys = max(LATENT_SPLIT_MIN_KEYS, -(-(-(-max_context // want)) // 32) * 32)
+        splits = -(-max_context // split_keys)
+        if splits > 1:
+            part_acc = torch.empty((T, heads, splits, rank), dtype=torch.float32, device=out.device)
+            part_ml = torch.empty((T, heads, splits, 2), dtype=torch.float32, device=out.device)
+        else:
+            split_keys = 0
     st = library("latent_attention").cj_latent_attention(_ptr(q_abs), _ptr(q_rot), _ptr(plane), _i(_code(plane)), _i(rank), _i(rot),
                                                          _i(heads), _i(T), _ptr(positions), _ptr(row_req), _ptr(table),
-                                                         _i(table.stride(0)), _i(page_tokens), _f(scale), _ptr(out), _stream())
+                                                         _i(table.stride(0)), _i(page_tokens), _f(scale), _ptr(out),
+                                                         _i(split_keys), _i(splits), _ptr(part_acc), _ptr(part_ml), _stream())
     _check(st, "latent_attention")
+    if split_keys:
+        global launches
+        launches += 1                  # the merge is a kernel of its own
 
 
 def latent_gate_out(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:

@@ -85,19 +85,28 @@ __global__ void latent_q_split_kernel(const float* __restrict__ q, int ld, int h
     }
 }
 
-// One block: one row, up to 8 heads (a warp each).  Keys come in chunks of 32 into shared
-// memory (a row of the chunk is padded to an odd number of 32-bit words, so that 32 lanes
-// reading 32 keys at one offset hit 32 banks); lane j of a warp scores key j for the warp's
-// head, the warp keeps the running maximum and sum, and for the weighted sum lane l owns
-// entries l, l + 32, ... of the latent.
+// One block: one row, up to 8 heads (a warp each), one stretch of the row's keys.  Keys come
+// in chunks of 32 into shared memory (a row of the chunk is padded to an odd number of 32-bit
+// words, so that 32 lanes reading 32 keys at one offset hit 32 banks); lane j of a warp scores
+// key j for the warp's head, the warp keeps the running maximum and sum, and for the weighted
+// sum a lane owns entries of the latent at a stride of 32 (pairs of them at a stride of 64
+// when the cache holds 16-bit entries: one 32-bit word a read).
+// With few rows in the step (decoding) the keys of a row are cut into stretches of split_keys,
+// one block each (blockIdx.z), which leave unnormalised sums, maxima and weights behind; a
+// second kernel merges them in stretch order.  How a row is cut depends on its position and
+// split_keys only.
 constexpr int LA_KEYS = 32;
 constexpr int LA_HEADS = 8;
+
+template <typename TC> struct Packed { static constexpr bool value = false; };
+template <> struct Packed<__nv_bfloat16> { static constexpr bool value = true; };
 
 template <typename TC, int NACC>
 __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
     const float* __restrict__ q_abs, const float* __restrict__ q_rot, const TC* __restrict__ plane, int rank, int rot,
     int heads, int T, const int* __restrict__ positions, const int* __restrict__ row_req, const int* __restrict__ table,
-    int table_stride, int page_tokens, float scale, TC* __restrict__ out, int row_words) {
+    int table_stride, int page_tokens, float scale, TC* __restrict__ out, int row_words, int split_keys,
+    float* __restrict__ part_acc, float* __restrict__ part_ml) {
     cj::after_predecessor();
     cj::release_successor();
     extern __shared__ __align__(16) unsigned char smem[];
@@ -110,6 +119,9 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
     const int head = blockIdx.y * LA_HEADS + warp;
     const bool has_head = head < heads;
     const int pos = positions[r];
+    const int key_begin = split_keys > 0 ? (int)blockIdx.z * split_keys : 0;
+    const int key_end = split_keys > 0 ? min(pos + 1, key_begin + split_keys) : pos + 1;
+    if (key_begin >= key_end) return;                            // this stretch lies past the row's position
     const int* pages = table + (size_t)row_req[r] * table_stride;
     if (has_head) {
         const float* qa = q_abs + ((size_t)head * T + r) * rank;
@@ -117,30 +129,31 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
         for (int i = lane; i < rank; i += 32) qs[warp * width + i] = qa[i];
         for (int i = lane; i < rot; i += 32) qs[warp * width + rank + i] = qr[i];
     }
+    // 16-bit entries, an even number of them in the latent and in the whole entry: two a word
+    const bool packed = Packed<TC>::value && (rank % 2 == 0) && (width % 2 == 0);
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
     float m = -INFINITY, l = 0.0f;
     const TC* krow_base = (const TC*)ks;
     const int row_elems = row_words * (int)(4 / sizeof(TC));
-    for (int k0 = 0; k0 <= pos; k0 += LA_KEYS) {
-        const int n_keys = min(LA_KEYS, pos + 1 - k0);
+    for (int k0 = key_begin; k0 < key_end; k0 += LA_KEYS) {
+        const int n_keys = min(LA_KEYS, key_end - k0);
         __syncthreads();                                        // the chunk before has been used up (and qs is written)
         // bring the chunk in: a key's entry is contiguous in its page
         if ((width * sizeof(TC)) % 4 == 0) {
             const int words = width * (int)sizeof(TC) / 4;
-            for (int i = threadIdx.x; i < n_keys * words; i += blockDim.x) {
-                const int j = i / words, e = i % words;
+            for (int j = warp; j < n_keys; j += LA_HEADS) {
                 const int kp = k0 + j;
                 const uint32_t* src = (const uint32_t*)(plane + ((size_t)pages[kp / page_tokens] * page_tokens + kp % page_tokens) * width);
-                ks[j * row_words + e] = src[e];
+                for (int e = lane; e < words; e += 32) ks[j * row_words + e] = src[e];
             }
         } else {
             TC* kd = (TC*)ks;
-            for (int i = threadIdx.x; i < n_keys * width; i += blockDim.x) {
-                const int j = i / width, e = i % width;
+            for (int j = warp; j < n_keys; j += LA_HEADS) {
                 const int kp = k0 + j;
-                kd[j * row_elems + e] = plane[((size_t)pages[kp / page_tokens] * page_tokens + kp % page_tokens) * width + e];
+                const TC* src = plane + ((size_t)pages[kp / page_tokens] * page_tokens + kp % page_tokens) * width;
+                for (int e = lane; e < width; e += 32) kd[j * row_elems + e] = src[e];
             }
         }
         __syncthreads();
@@ -148,10 +161,21 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
         // scores: lane j, key j
         float s = -INFINITY;
         if (lane < n_keys) {
-            const TC* kr = krow_base + (size_t)lane * row_elems;
             const float* qh = qs + warp * width;
             float dot = 0.0f;
-            for (int e = 0; e < width; ++e) dot = fmaf(qh[e], to_f32(kr[e]), dot);
+            if (packed) {
+                const uint32_t* kw = ks + (size_t)lane * row_words;
+                float dot2 = 0.0f;
+                for (int e = 0; e < width / 2; ++e) {
+                    const uint32_t w2 = kw[e];
+                    dot = fmaf(qh[2 * e], __uint_as_float(w2 << 16), dot);
+                    dot2 = fmaf(qh[2 * e + 1], __uint_as_float(w2 & 0xffff0000u), dot2);
+                }
+                dot += dot2;
+            } else {
+                const TC* kr = krow_base + (size_t)lane * row_elems;
+                for (int e = 0; e < width; ++e) dot = fmaf(qh[e], to_f32(kr[e]), dot);
+            }
             s = dot * scale;
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -163,25 +187,71 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < NACC; ++i) acc[i] *= corr;
-        for (int j = 0; j < n_keys; ++j) {
-            const float pw = ps[warp * LA_KEYS + j];
-            const TC* kr = krow_base + (size_t)j * row_elems;
+        if (packed) {
+            for (int j = 0; j < n_keys; ++j) {
+                const float pw = ps[warp * LA_KEYS + j];
+                const uint32_t* kw = ks + (size_t)j * row_words;
 #pragma unroll
-            for (int i = 0; i < NACC; ++i) {
-                const int e = lane + 32 * i;
-                if (e < rank) acc[i] = fmaf(pw, to_f32(kr[e]), acc[i]);
+                for (int i = 0; i < NACC / 2; ++i) {
+                    const int e = 2 * lane + 64 * i;
+                    if (e < rank) {
+                        const uint32_t w2 = kw[lane + 32 * i];
+                        acc[2 * i] = fmaf(pw, __uint_as_float(w2 << 16), acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(pw, __uint_as_float(w2 & 0xffff0000u), acc[2 * i + 1]);
+                    }
+                }
+            }
+        } else {
+            for (int j = 0; j < n_keys; ++j) {
+                const float pw = ps[warp * LA_KEYS + j];
+                const TC* kr = krow_base + (size_t)j * row_elems;
+#pragma unroll
+                for (int i = 0; i < NACC; ++i) {
+                    const int e = lane + 32 * i;
+                    if (e < rank) acc[i] = fmaf(pw, to_f32(kr[e]), acc[i]);
+                }
             }
         }
         __syncwarp();
     }
-    if (has_head) {
-        TC* dst = out + ((size_t)head * T + r) * rank;
-        const float inv = 1.0f / l;
+    if (!has_head) return;
+    const size_t item = (size_t)r * heads + head;
+    float* pacc = part_acc ? part_acc + (item * gridDim.z + blockIdx.z) * rank : nullptr;
+    if (pacc && lane == 0) {
+        part_ml[(item * gridDim.z + blockIdx.z) * 2] = m;
+        part_ml[(item * gridDim.z + blockIdx.z) * 2 + 1] = l;
+    }
+    TC* dst = out + ((size_t)head * T + r) * rank;
+    const float inv = 1.0f / l;
 #pragma unroll
-        for (int i = 0; i < NACC; ++i) {
-            const int e = lane + 32 * i;
-            if (e < rank) dst[e] = from_f32<TC>(acc[i] * inv);
+    for (int i = 0; i < NACC; ++i) {
+        const int e = packed ? 2 * lane + 64 * (i / 2) + (i & 1) : lane + 32 * i;
+        if (e < rank) {
+            if (pacc) pacc[e] = acc[i];
+            else dst[e] = from_f32<TC>(acc[i] * inv);
         }
+    }
+}
+
+// the stretches of a row's keys, merged in order: out = sum_z e^(m_z - M) acc_z / sum_z e^(m_z - M) l_z
+template <typename TC>
+__global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int splits, int split_keys,
+                                    int rank, int heads, int T, const int* __restrict__ positions, TC* __restrict__ out) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int r = blockIdx.x, head = blockIdx.y;
+    const int nz = min(splits, (positions[r] + split_keys) / split_keys);
+    const size_t item = (size_t)r * heads + head;
+    const float* ml = part_ml + item * splits * 2;
+    float M = -INFINITY;
+    for (int z = 0; z < nz; ++z) M = fmaxf(M, ml[2 * z]);
+    float L = 0.0f;
+    for (int z = 0; z < nz; ++z) L += expf(ml[2 * z] - M) * ml[2 * z + 1];
+    const float inv = 1.0f / L;
+    for (int e = threadIdx.x; e < rank; e += blockDim.x) {
+        float v = 0.0f;
+        for (int z = 0; z < nz; ++z) v = fmaf(expf(ml[2 * z] - M), part_acc[(item * splits + z) * rank + e], v);
+        out[((size_t)head * T + r) * rank + e] = from_f32<TC>(v * inv);
     }
 }
 
@@ -225,21 +295,28 @@ CJ_EXPORT int cj_latent_q_split(const float* q, int ld, int heads, int dim, int 
     return launch_status();
 }
 
+// split_keys > 0: a row's keys are cut into stretches of that many (a multiple of 32), one block each;
+// part_acc [T, heads, splits, rank] and part_ml [T, heads, splits, 2] (float32) then hold the
+// stretches' results, splits = ceil(max_context / split_keys).  split_keys = 0: one block a row.
 CJ_EXPORT int cj_latent_attention(const float* q_abs, const float* q_rot, const void* plane, int cache_dtype, int rank, int rot,
                                   int heads, int T, const int* positions, const int* row_req, const int* table, int table_stride,
-                                  int page_tokens, float scale, void* out, cudaStream_t stream) {
+                                  int page_tokens, float scale, void* out, int split_keys, int splits, float* part_acc,
+                                  float* part_ml, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!q_abs || !q_rot || !plane || !positions || !row_req || !table || !out) return CJ_ERR_ARG;
     if (rank <= 0 || rank > 1024 || rot < 0 || heads <= 0 || page_tokens <= 0) return CJ_ERR_SIZE;
+    if (split_keys < 0 || split_keys % LA_KEYS != 0 || (split_keys > 0 && (splits < 1 || splits > 65535 || !part_acc || !part_ml))) return CJ_ERR_ARG;
     const int width = rank + rot;
     const int esize = cache_dtype == CJ_F32 ? 4 : 2;
     int row_words = (width * esize + 3) / 4;
     if ((row_words & 1) == 0) row_words += 1;
     const size_t smem = (size_t)LA_HEADS * width * 4 + (size_t)LA_HEADS * LA_KEYS * 4 + (size_t)LA_KEYS * row_words * 4;
     if (smem > 200 * 1024) return CJ_ERR_SIZE;
-    dim3 grid(T, (heads + LA_HEADS - 1) / LA_HEADS);
+    dim3 grid(T, (heads + LA_HEADS - 1) / LA_HEADS, split_keys > 0 ? splits : 1);
     if (grid.y > 65535) return CJ_ERR_SIZE;
     const int nacc = (rank + 31) / 32;
+    float* pa = split_keys > 0 ? part_acc : nullptr;
+    float* pm = split_keys > 0 ? part_ml : nullptr;
 #define LAUNCH(TC, N)                                                                                                  \
     do {                                                                                                               \
         static bool sized_##N = false;                                                                                 \
@@ -248,7 +325,11 @@ CJ_EXPORT int cj_latent_attention(const float* q_abs, const float* q_rot, const 
             sized_##N = true;                                                                                          \
         }                                                                                                              \
         cj::launch(latent_attention_kernel<TC, N>, grid, dim3(LA_HEADS * 32), smem, stream, q_abs, q_rot, (const TC*)plane, \
-                   rank, rot, heads, T, positions, row_req, table, table_stride, page_tokens, scale, (TC*)out, row_words);  \
+                   rank, rot, heads, T, positions, row_req, table, table_stride, page_tokens, scale, (TC*)out, row_words, \
+                   split_keys, pa, pm);                                                                                \
+        if (split_keys > 0)                                                                                            \
+            cj::launch(latent_merge_kernel<TC>, dim3(T, heads), dim3(128), 0, stream, (const float*)pa, (const float*)pm, splits, \
+                       split_keys, rank, heads, T, positions, (TC*)out);                                               \
     } while (0)
 #define PICK(TC)                                  \
     do {                                          \

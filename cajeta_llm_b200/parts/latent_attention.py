@@ -122,7 +122,7 @@ class LatentAttention(Part):
         lat = torch.empty((H * T, self.rank), dtype=rt.cache_dtype, device=dev)
         K.tag = "attention"
         K.latent_attention(q_abs, q_rot, entry.k_plane, self.rank, self.rot, H, ctx.positions, ctx.row_req, entry.block_table,
-                           entry.page_tokens, self.scale, lat)
+                           entry.page_tokens, self.scale, lat, max_context=ctx.max_context)
         o = torch.empty((H * T, self.vdim), dtype=torch.float32, device=dev)
         K.tag = "value up"
         project(rt, lat, self.w_uv, o, group_offsets=offsets, max_group_rows=T, offsets_settled=True)

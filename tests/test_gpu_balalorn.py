@@ -303,3 +303,62 @@ def test_replay_tool_on_a_model_folder(folders, tmp_path):
     check(got[0], wa[10:11], "float32", "step 0")
     check(got[1], wb[8:9], "float32", "step 1")
     check(got[2], wa[[11, 19]], "float32", "step 2")
+
+
+def random_config(seed):
+    """A configuration drawn at random: layer order, every size, which layers share a latent cache."""
+    rng = random.Random(seed)
+    width = rng.choice([40, 72, 136, 256])
+    big = width >= 128
+
+    def pick(lo, hi):
+        return rng.randint(lo, hi)
+
+    layers, owners = [], []
+    for i in range(rng.randint(2, 5)):
+        kind = rng.choice(["latent_attention", "mamba2", "delta"])
+        if kind == "latent_attention":
+            rot_dim = 2 * pick(1, 8)
+            m = {"heads": pick(1, 10), "dim": rng.choice([128, 136]) if big and rng.random() < 0.4 else pick(3, 40), "rot_dim": rot_dim,
+                 "vdim": rng.choice([128, 144]) if big and rng.random() < 0.4 else pick(3, 40),
+                 "kv_rank": rng.choice([128, 160]) if big and rng.random() < 0.5 else pick(5, 70),
+                 "scale": rng.choice([0.1, 0.3, 1.0]), "rot": {"base": rng.choice([100.0, 10000.0, 500000.0]), "dims": 2 * pick(1, rot_dim // 2)}}
+            if owners and rng.random() < 0.5:
+                j = rng.choice(owners)
+                src = layers[j]["mixer"]
+                m.update(kv_from=j, kv_rank=src["kv_rank"], rot_dim=src["rot_dim"], rot=dict(src["rot"]))
+            else:
+                owners.append(i)
+        elif kind == "mamba2":
+            g = pick(1, 3)
+            heads, vdim = g * pick(1, 3), pick(3, 24)
+            divisors = [d for d in range(1, heads * vdim + 1) if (heads * vdim) % d == 0 and d <= 8]
+            m = {"heads": heads, "vdim": vdim, "state": pick(2, 70), "groups": g, "norm_groups": rng.choice(divisors), "conv": pick(1, 5)}
+        else:
+            kv = pick(1, 3)
+            m = {"heads": kv * pick(1, 3), "kv_heads": kv, "dim": pick(3, 70), "vdim": pick(3, 40), "conv": pick(1, 5)}
+        ff = rng.choice([None, "dense", "moe", "moe"])
+        if ff == "dense":
+            mlp = {"kind": "dense", "ff": rng.choice([pick(8, 60), 128, 200]) if big else pick(8, 60)}
+        elif ff == "moe":
+            e = pick(1, 9)
+            mlp = {"kind": "moe", "expert": {"ff": rng.choice([pick(8, 60), 128, 136]) if big else pick(8, 60)},
+                   "router": {"experts": e, "top": pick(1, e)}}
+        else:
+            mlp = None
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    return config_of(layers, width=width, vocab=rng.choice([70, 131, 300]), eps=rng.choice([1e-5, 1e-6]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(folders, seed):
+    raw = random_config(1000 + seed)
+    d, (cfg, W) = folders(f"random{seed}", raw, seed=100 + seed)
+    toks = helpers.random_tokens(cfg["vocab"], 45, seed=seed)
+    want, _ = P.forward(toks, W, cfg)
+    for dtype in ("float32", "bfloat16"):
+        r = runner_for(d, dtype, max_tokens=64)
+        for cuts in ([45], [17, 2, 9] + [1] * 17):
+            s = r.admit()
+            check(feed(r, s, toks, cuts), want, dtype, f"{json.dumps(raw['layers'])} {dtype} cuts {cuts[:3]}")
+            r.release(s)
