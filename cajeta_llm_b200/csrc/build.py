@@ -44,6 +44,7 @@ LIBRARIES: Dict[str, str] = {
     "random_fill": "random_fill.cu",
     "recurrent": "recurrent.cu",
     "latent_attention": "latent_attention.cu",
+    "latent_prefill": "latent_prefill.cu",
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 

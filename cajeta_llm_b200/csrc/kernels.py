@@ -486,7 +486,7 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tens
     blocks = T * -(-heads // 8)
     split_keys, splits, part_acc, part_ml = 0, 1, None, None
     if max_context > LATENT_SPLIT_MIN_KEYS and blocks < LATENT_FILL_BLOCKS:
-        want = -(-LATENT_FILL_BLOCKS // blocks)
+        want = min(64, -(-LATENT_FILL_BLOCKS // blocks))
         split_keys = max(LATENT_SPLIT_MIN_KEYS, -(-(-(-max_context // want)) // 32) * 32)
         splits = -(-max_context // split_keys)
         if splits > 1:
@@ -502,6 +502,65 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, plane: torch.Tens
     if split_keys:
         global launches
         launches += 1                  # the merge is a kernel of its own
+
+
+# -- the plain form for long prompt portions: keys and values built per head, a flash kernel over them --
+def latent_gather(plane: torch.Tensor, rank: int, tok_req: torch.Tensor, tok_pos: torch.Tensor, table: torch.Tensor,
+                  page_tokens: int, c_all: torch.Tensor) -> None:
+    """c_all[n] = the latent of (request tok_req[n], position tok_pos[n]) from the paged cache; bfloat16."""
+    _need(plane, "plane", torch.bfloat16), _need(c_all, "c_all", torch.bfloat16), _need(table, "table", torch.int32)
+    _need(tok_req, "tok_req", torch.int32), _need(tok_pos, "tok_pos", torch.int32)
+    st = library("latent_prefill").cj_latent_gather(_ptr(plane), _i(plane.shape[-1]), _i(rank), _ptr(tok_req), _ptr(tok_pos), _ptr(table),
+                                                    _i(table.stride(0)), _i(page_tokens), _ptr(c_all), _i(tok_req.numel()), _stream())
+    _check(st, "latent_gather")
+
+
+def latent_kv_pack(kp: torch.Tensor, vp: torch.Tensor, plane: torch.Tensor, rank: int, rot: int, tok_req: torch.Tensor,
+                   tok_pos: torch.Tensor, table: torch.Tensor, page_tokens: int, heads: int, dim: int, vdim: int,
+                   kx: torch.Tensor, vx: torch.Tensor) -> None:
+    """kx[n, h] = [kp[n, h] | the cached rotated key part of token n | 0], vx[n, h] = [vp[n, h] | 0]; bfloat16."""
+    for n, t in (("kp", kp), ("vp", vp), ("plane", plane), ("kx", kx), ("vx", vx)):
+        _need(t, n, torch.bfloat16)
+    _need(tok_req, "tok_req", torch.int32), _need(tok_pos, "tok_pos", torch.int32), _need(table, "table", torch.int32)
+    N = tok_req.numel()
+    if kp.numel() != N * heads * dim or vp.numel() != N * heads * vdim or kx.shape[:2] != (N, heads) or vx.shape[:2] != (N, heads):
+        raise KernelError("latent_kv_pack: sizes do not agree")
+    st = library("latent_prefill").cj_latent_kv_pack(_ptr(kp), _ptr(vp), _ptr(plane), _i(plane.shape[-1]), _i(rank), _i(rot), _ptr(tok_req),
+                                                     _ptr(tok_pos), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(heads), _i(dim),
+                                                     _i(vdim), _i(kx.shape[2]), _i(vx.shape[2]), _ptr(kx), _ptr(vx), _i(N), _stream())
+    _check(st, "latent_kv_pack")
+
+
+def latent_q_pack(q: torch.Tensor, heads: int, dim: int, rot: int, rotary: int, inv_freq: Optional[torch.Tensor],
+                  positions: torch.Tensor, qx: torch.Tensor) -> None:
+    """qx[t, h] = [q[t, h, :dim] | rotate(q[t, h, dim:]) | 0] in bfloat16; q float32 [T, >= heads (dim + rot)]."""
+    _need(q, "q", torch.float32), _need(qx, "qx", torch.bfloat16), _need(positions, "positions", torch.int32)
+    st = library("latent_prefill").cj_latent_q_pack(_ptr(q), _i(q.stride(0)), _i(heads), _i(dim), _i(rot), _i(rotary), _ptr(inv_freq),
+                                                    _ptr(positions), _i(qx.shape[2]), _ptr(qx), _i(q.shape[0]), _stream())
+    _check(st, "latent_q_pack")
+
+
+def latent_flash(qx: torch.Tensor, out: torch.Tensor, kx: torch.Tensor, vx: torch.Tensor, req_start: torch.Tensor,
+                 req_prior: torch.Tensor, req_base: torch.Tensor, requests: int, heads: int, scale: float) -> None:
+    """Causal attention of the step's rows (request i: rows [req_start[i], req_start[i+1]) at positions
+    req_prior[i] + j) over the dense keys and values of their requests (request i's token p at
+    req_base[i] + p).  qx [T, heads, DK], kx [N, heads, DK], vx [N, heads, DV], out [T, heads, DV], bfloat16."""
+    for n, t in (("qx", qx), ("out", out), ("kx", kx), ("vx", vx)):
+        _need(t, n, torch.bfloat16)
+    for n, t in (("req_start", req_start), ("req_prior", req_prior), ("req_base", req_base)):
+        _need(t, n, torch.int32)
+    st = library("latent_prefill").cj_latent_flash(_ptr(qx), _ptr(out), _ptr(kx), _ptr(vx), _ptr(req_start), _ptr(req_prior), _ptr(req_base),
+                                                   _i(requests), _i(qx.shape[0]), _i(heads), _i(qx.shape[2]), _i(vx.shape[2]), _f(scale),
+                                                   _stream())
+    _check(st, "latent_flash")
+
+
+def latent_gate_rows(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:
+    """out[t, h * vdim + e] = o[t, h, e] * sigmoid(gate[t, gate_offset + h]); o bfloat16 [T, heads, DV], gate float32."""
+    _need(o, "o", torch.bfloat16), _need(gate, "gate", torch.float32), _need(out, "out", torch.bfloat16)
+    st = library("latent_prefill").cj_latent_gate_rows(_ptr(o), _i(o.shape[2]), ctypes.c_void_p(gate.data_ptr() + 4 * gate_offset),
+                                                       _i(gate.stride(0)), _i(heads), _i(vdim), _ptr(out), _i(o.shape[0]), _stream())
+    _check(st, "latent_gate_rows")
 
 
 def latent_gate_out(o: torch.Tensor, gate: torch.Tensor, gate_offset: int, heads: int, vdim: int, out: torch.Tensor) -> None:

@@ -20,8 +20,8 @@
 // The two scans give a thread one column of the state (one value dimension) for a share of
 // its rows: a block is (request, head, tile of columns), a column's rows are dealt to DP
 // neighbouring lanes, each holding NPER of them in registers, and a sum over the rows is a
-// butterfly over those lanes.  Columns never talk to each other, so a block needs no
-// barrier; the tokens of a request are walked in order, which is what makes the result
+// butterfly over those lanes.  Columns never talk to each other; the block's barriers only
+// guard the staging of the tokens' inputs.  The tokens of a request are walked in order, which is what makes the result
 // independent of how a prompt was cut: the state after token t is the same sequence of
 // float32 operations whether t ended a step or not.
 #include "common.cuh"
@@ -142,92 +142,138 @@ struct ScanArgs {
     float q_scale;
 };
 
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A token's inputs (the two vectors over the state's rows, the block's columns of the value
+// vector, the two gate inputs) are staged in shared memory TOK tokens at a time, the next
+// TOK in flight (cp.async) while these are walked: a token's step then waits on shared
+// memory, not on a round trip to L2.  One staged token: [a: rows | b: rows | v: block's columns | 2].
 template <int NPER, bool DELTA>
-__global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP) {
+__global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) {
     cj::after_predecessor();
     cj::release_successor();
+    extern __shared__ __align__(16) float staged[];
     const int req = blockIdx.x, head = blockIdx.y;
     const int slot = p.req_slot[req];
     const int first = p.req_start[req], n = p.req_start[req + 1] - first;
     if (slot < 0 || n <= 0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int cols_per_warp = 32 / DP;
+    const int cols_per_warp = 32 / DP, cols_blk = 4 * cols_per_warp;
     const int part = lane / cols_per_warp;                  // which share of the state's rows
-    const int col = blockIdx.z * (4 * cols_per_warp) + warp * cols_per_warp + (lane % cols_per_warp);
+    const int col0 = blockIdx.z * cols_blk;
+    const int lcol = warp * cols_per_warp + (lane % cols_per_warp);
+    const int col = col0 + lcol;
     const bool live = col < p.cols;
+    const int rows = p.rows;
     const int group = head / (p.heads / p.groups);
-    float* S = p.state + (size_t)slot * p.slot_stride + (size_t)head * p.rows * p.cols;
+    const int stride = 2 * rows + cols_blk + 2;
+    float* S = p.state + (size_t)slot * p.slot_stride + (size_t)head * rows * p.cols;
+
+    auto stage = [&](int chunk, float* buf) {
+        const int t0 = chunk * TOK, nt = min(TOK, n - t0);
+        for (int i = threadIdx.x; i < nt * stride; i += 128) {
+            const int tt = i / stride, e = i - tt * stride;
+            const size_t row = (size_t)(first + t0 + tt);
+            const float* src = nullptr;
+            if (e < rows) src = p.x + row * p.ld + p.off_a + group * rows + e;
+            else if (e < 2 * rows) src = p.x + row * p.ld + p.off_b + group * rows + (e - rows);
+            else if (e < 2 * rows + cols_blk) {
+                const int c = col0 + e - 2 * rows;
+                if (c < p.cols) src = p.x + row * p.ld + p.off_v + head * p.cols + c;
+            } else if (e == 2 * rows + cols_blk) src = p.raw + row * p.ld_raw + p.off_dt + head;
+            else if (DELTA) src = p.raw + row * p.ld_raw + p.off_beta + head;
+            if (src) cp_async4(buf + i, src);
+            else buf[i] = 0.0f;
+        }
+    };
+
+    const int chunks = (n + TOK - 1) / TOK;
+    stage(0, staged);
+    cp_async_commit();
     float s[NPER];
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
         const int d = part + DP * i;
-        s[i] = (live && d < p.rows) ? S[(size_t)d * p.cols + col] : 0.0f;
+        s[i] = (live && d < rows) ? S[(size_t)d * p.cols + col] : 0.0f;
     }
     const float A = expf(p.A_log[head]);
     const float bias = p.dt_bias[head];
     const float skip = DELTA ? 0.0f : p.skip[head];
-    for (int t = 0; t < n; ++t) {
-        const float* xr = p.x + (size_t)(first + t) * p.ld;
-        const float* rr = p.raw + (size_t)(first + t) * p.ld_raw;
-        const float* ra = xr + p.off_a + group * p.rows;
-        const float* rb = xr + p.off_b + group * p.rows;
-        const float xv = live ? xr[p.off_v + head * p.cols + col] : 0.0f;
-        float a[NPER], b[NPER];
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+        float* cur = staged + (chunk & 1) * TOK * stride;
+        if (chunk + 1 < chunks) stage(chunk + 1, staged + ((chunk + 1) & 1) * TOK * stride);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int nt = min(TOK, n - chunk * TOK);
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* tk = cur + tt * stride;
+            const int t = chunk * TOK + tt;
+            const float xv = tk[2 * rows + lcol];
+            const float g0 = tk[2 * rows + cols_blk], g1 = tk[2 * rows + cols_blk + 1];
+            float a[NPER], b[NPER];
 #pragma unroll
-        for (int i = 0; i < NPER; ++i) {
-            const int d = part + DP * i;
-            a[i] = d < p.rows ? ra[d] : 0.0f;
-            b[i] = d < p.rows ? rb[d] : 0.0f;
+            for (int i = 0; i < NPER; ++i) {
+                const int d = part + DP * i;
+                a[i] = d < rows ? tk[d] : 0.0f;
+                b[i] = d < rows ? tk[rows + d] : 0.0f;
+            }
+            if (DELTA) {
+                // a = q, b = k: unit vectors per head, q also times rows^(-1/2)
+                float qq = 0.0f, kk = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) { qq = fmaf(a[i], a[i], qq); kk = fmaf(b[i], b[i], kk); }
+                for (int o = cols_per_warp; o < 32; o <<= 1) {
+                    qq += __shfl_xor_sync(0xffffffffu, qq, o);
+                    kk += __shfl_xor_sync(0xffffffffu, kk, o);
+                }
+                const float qs = p.q_scale / sqrtf(qq + 1e-6f), ks = 1.0f / sqrtf(kk + 1e-6f);
+                const float decay = expf(-A * softplus_f(g0 + bias));
+                const float beta = sigmoid_f(g1);
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    a[i] *= qs;
+                    b[i] *= ks;
+                    s[i] *= decay;
+                    dot = fmaf(s[i], b[i], dot);
+                }
+                for (int o = cols_per_warp; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                const float u = beta * (xv - dot);
+                float y = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    s[i] = fmaf(b[i], u, s[i]);
+                    y = fmaf(s[i], a[i], y);
+                }
+                for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+                if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = y;
+            } else {
+                // a = B, b = C
+                const float dt = softplus_f(g0 + bias);
+                const float decay = expf(-A * dt);
+                const float dx = dt * xv;
+                float y = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    s[i] = fmaf(decay, s[i], a[i] * dx);
+                    y = fmaf(s[i], b[i], y);
+                }
+                for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+                if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = fmaf(skip, xv, y);
+            }
         }
-        if (DELTA) {
-            // a = q, b = k: unit vectors per head, q also times rows^(-1/2)
-            float qq = 0.0f, kk = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NPER; ++i) { qq = fmaf(a[i], a[i], qq); kk = fmaf(b[i], b[i], kk); }
-            for (int o = cols_per_warp; o < 32; o <<= 1) {
-                qq += __shfl_xor_sync(0xffffffffu, qq, o);
-                kk += __shfl_xor_sync(0xffffffffu, kk, o);
-            }
-            const float qs = p.q_scale / sqrtf(qq + 1e-6f), ks = 1.0f / sqrtf(kk + 1e-6f);
-            const float decay = expf(-A * softplus_f(rr[p.off_dt + head] + bias));
-            const float beta = sigmoid_f(rr[p.off_beta + head]);
-            float dot = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NPER; ++i) {
-                a[i] *= qs;
-                b[i] *= ks;
-                s[i] *= decay;
-                dot = fmaf(s[i], b[i], dot);
-            }
-            for (int o = cols_per_warp; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = beta * (xv - dot);
-            float y = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NPER; ++i) {
-                s[i] = fmaf(b[i], u, s[i]);
-                y = fmaf(s[i], a[i], y);
-            }
-            for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = y;
-        } else {
-            // a = B, b = C
-            const float dt = softplus_f(rr[p.off_dt + head] + bias);
-            const float decay = expf(-A * dt);
-            const float dx = dt * xv;
-            float y = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NPER; ++i) {
-                s[i] = fmaf(decay, s[i], a[i] * dx);
-                y = fmaf(s[i], b[i], y);
-            }
-            for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = fmaf(skip, xv, y);
-        }
+        __syncthreads();                       // everyone has walked this buffer before it is staged into again
     }
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
         const int d = part + DP * i;
-        if (live && d < p.rows) S[(size_t)d * p.cols + col] = s[i];
+        if (live && d < rows) S[(size_t)d * p.cols + col] = s[i];
     }
 }
 
@@ -337,9 +383,9 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
     if (!x || !raw || !A_log || !dt_bias || !state || !req_start || !req_slot || !out) return CJ_ERR_ARG;
     if (mode == 0 && !skip) return CJ_ERR_ARG;
     if (heads <= 0 || groups <= 0 || heads % groups != 0 || rows <= 0 || cols <= 0) return CJ_ERR_SIZE;
-    // a column's rows are dealt to DP lanes with at most 64 rows each
+    // a column's rows are dealt to DP lanes: about 8 rows a lane where 32 lanes allow it, at most 64
     int DP = 4;
-    while (DP < 32 && (rows + DP - 1) / DP > 64) DP <<= 1;
+    while (DP < 32 && (rows + DP - 1) / DP > 8) DP <<= 1;
     const int per = (rows + DP - 1) / DP;
     if (per > 64) return CJ_ERR_SIZE;
     ScanArgs p{x, ld, off_a, off_b, off_v, raw, ld_raw, off_dt, off_beta, A_log, dt_bias, skip, state, slot_stride,
@@ -347,10 +393,22 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
     const int cols_per_block = 4 * (32 / DP);
     dim3 grid(requests, heads, (cols + cols_per_block - 1) / cols_per_block);
     if (grid.y > 65535 || grid.z > 65535) return CJ_ERR_SIZE;
-#define LAUNCH(N)                                                                                   \
-    do {                                                                                            \
-        if (mode == 0) cj::launch(scan_kernel<N, false>, grid, dim3(128), 0, stream, p, DP);        \
-        else cj::launch(scan_kernel<N, true>, grid, dim3(128), 0, stream, p, DP);                   \
+    // tokens staged at a time: up to 16, as many as 96 KB of shared memory hold twice
+    const size_t token_bytes = (size_t)(2 * rows + cols_per_block + 2) * sizeof(float);
+    int TOK = (int)((96 * 1024) / (2 * token_bytes));
+    if (TOK > 16) TOK = 16;
+    if (TOK < 1) return CJ_ERR_SIZE;
+    const size_t smem = 2 * (size_t)TOK * token_bytes;
+#define LAUNCH(N)                                                                                                       \
+    do {                                                                                                                \
+        static bool sized = false;                                                                                      \
+        if (!sized) {                                                                                                   \
+            cudaFuncSetAttribute(scan_kernel<N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);        \
+            cudaFuncSetAttribute(scan_kernel<N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);         \
+            sized = true;                                                                                               \
+        }                                                                                                               \
+        if (mode == 0) cj::launch(scan_kernel<N, false>, grid, dim3(128), smem, stream, p, DP, TOK);                    \
+        else cj::launch(scan_kernel<N, true>, grid, dim3(128), smem, stream, p, DP, TOK);                               \
     } while (0)
     if (per <= 8) LAUNCH(8);
     else if (per <= 16) LAUNCH(16);

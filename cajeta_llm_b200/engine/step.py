@@ -150,6 +150,9 @@ class ModelRunner:
         mixers = [model.blocks[e.layer].mixer for e in model.plan.schedule]
         graph_safe = all(getattr(m, "graph_safe", m.state_need() is None) for m in mixers)
         self.cuda_graphs = cuda_graphs and graph_safe and self.runtime.fast_kernels and self.runtime.device.type == "cuda"
+        # a mixer may run steps of many rows in a form that reads the requests' lengths on the host
+        # (``capture_max_rows``): steps with more rows than that are launched kernel by kernel
+        self.capture_max_rows = min([int(getattr(m, "capture_max_rows", 1 << 30)) for m in mixers] or [1 << 30])
         # what this model needs is compiled now, side by side (a library not named here is still
         # compiled when it is first wanted)
         if str(self.runtime.device).startswith("cuda"):
@@ -195,7 +198,7 @@ class ModelRunner:
             logits = self._forward(ctx)
         elif self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
             return self._step_captured(entries)
-        elif self.cuda_graphs:
+        elif self.cuda_graphs and sum(len(e.tokens) for e in entries) <= self.capture_max_rows:
             logits = self._step_mixed(entries)
         else:
             logits = self._forward(self._prepare(entries))

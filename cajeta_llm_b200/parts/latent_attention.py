@@ -15,7 +15,13 @@ The rotation pairs entries (2i, 2i+1) of the first ``rotary_dim`` entries of the
 part (the position part's ``rotary_dim`` and ``inv_freq``).  Nothing per head is built from
 the cache: ``W_uk[h]^T q`` is taken on the query's side and ``W_uv[h]`` applied to the
 weighted sum of latents, so the attention kernel reads each cache entry once for all
-heads.  An entry that reads another entry's cache (``entry.writes_cache`` false) has no
+heads.  Steps that carry long prompt portions on the bfloat16 path take the plain form
+instead (``EXPAND_MIN_ROWS`` rows or more): keys ``[W_uk[h] c | r]`` and values ``W_uv[h] c`` of
+the requests' tokens are built with two products over the gathered latents and a flash
+kernel on the tensor cores runs over them - a (query, key, head) pair then costs
+``2 (dim + rot_dim + vdim)`` flops instead of ``2 (2 kv_rank + rot_dim)``.  Such a step reads
+the requests' lengths on the host, so it is not captured into a CUDA graph
+(``capture_max_rows``).  An entry that reads another entry's cache (``entry.writes_cache`` false) has no
 ``W_dkv`` of its own: it attends over that entry's latents and key parts with its own
 queries, ``W_uk`` and ``W_uv``.
 
@@ -27,6 +33,7 @@ from __future__ import annotations
 
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 from ..csrc import kernels as K
@@ -37,6 +44,8 @@ from .plan import ParamSpec
 
 @register_part("mixer", "latent_attention")
 class LatentAttention(Part):
+    EXPAND_MIN_ROWS = 256       # steps with at least this many rows (and prompt portions) take the plain form
+
     def __init__(self, spec, prefix, runtime):
         super().__init__(spec, prefix, runtime)
         self.hidden = int(spec["hidden_size"])
@@ -55,7 +64,17 @@ class LatentAttention(Part):
         if self.rank > 1024:
             raise ValueError(f"kv_rank {self.rank} is larger than the attention kernel takes (1024)")
         self.nq = self.heads * (self.dim + self.rot)
-        self.w_in = self.w_norm = self.w_uk_t = self.w_uv = self.w_o = None
+        self.w_in = self.w_norm = self.w_uk_t = self.w_uv = self.w_o = self.w_uk = None
+        # the plain form's head sizes, padded to what its kernel is built for
+        self.dk_pad = -(-(self.dim + self.rot) // 64) * 64
+        self.dv_pad = -(-self.vdim // 64) * 64
+        self.can_expand = runtime.fast_kernels and self.dk_pad <= 256 and self.dv_pad <= 128
+
+    @property
+    def capture_max_rows(self) -> int:
+        """Steps with more rows than this are launched kernel by kernel: the plain form lays out the
+        requests' tokens from their lengths on the host."""
+        return self.EXPAND_MIN_ROWS - 1 if self.can_expand else 1 << 30
 
     def cache_need(self) -> Optional[KvNeed]:
         return KvNeed(1, self.rank + self.rot, 0, values=False)
@@ -77,7 +96,7 @@ class LatentAttention(Part):
         return p
 
     def libraries(self) -> set:
-        libs = {"latent_attention", "gemm_simt"}
+        libs = {"latent_attention", "gemm_simt"} | ({"latent_prefill"} if self.can_expand else set())
         if self.runtime.fast_kernels and self.hidden >= 128:
             libs |= {"gemm_tc", "gemm_tc2"}
         return libs
@@ -91,6 +110,7 @@ class LatentAttention(Part):
         uk = self.fetch(source, self.name("uk"))
         # head h's W_uk^T as the weight of a product over dim: [heads, kv_rank, dim]
         self.w_uk_t = uk.view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uk = uk if self.can_expand else None               # as stored: the plain form's product over kv_rank
         self.w_uv = self.fetch(source, self.name("uv")).view(self.heads, self.vdim, self.rank).contiguous()
         self.w_o = self.fetch(source, self.name("o"))
 
@@ -110,6 +130,20 @@ class LatentAttention(Part):
             K.tag = "latent norm + rope + cache write"
             K.latent_kv_write(proj, self.nq + H, self.rank, self.rot, self.rotary, self.w_norm, self.eps, inv_freq,
                               ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens, entry.k_plane)
+        if self.can_expand and T >= self.EXPAND_MIN_ROWS and not ctx.all_single and len(ctx.h_req_prior) > 0:
+            gated = self._plain_form(proj, ctx, entry)
+        else:
+            gated = self._absorbed_form(proj, ctx, entry)
+        K.tag = "o"
+        project(rt, gated, self.w_o, residual, accumulate=True)
+        K.tag = None
+        return None
+
+    def _absorbed_form(self, proj: torch.Tensor, ctx, entry) -> torch.Tensor:
+        rt = self.runtime
+        dev = proj.device
+        T, H = proj.shape[0], self.heads
+        inv_freq = self.position.inv_freq
         q_plain = torch.empty((H * T, self.dim), dtype=rt.act_dtype, device=dev)
         q_rot = torch.empty((T, H, self.rot), dtype=torch.float32, device=dev)
         K.tag = "q split + rope"
@@ -121,15 +155,59 @@ class LatentAttention(Part):
         project(rt, q_plain, self.w_uk_t, q_abs, group_offsets=offsets, max_group_rows=T)
         lat = torch.empty((H * T, self.rank), dtype=rt.cache_dtype, device=dev)
         K.tag = "attention"
+        # How far a row's keys can reach, as a number that a captured step may keep: a decode step's
+        # context (its graph is keyed by the context's bucket), otherwise what the block table spans
+        # (laid out at its full width in steps that are captured).  It only decides into how many
+        # stretches a row's keys are cut when the step has few rows.
+        reach = ctx.max_context if ctx.all_single else entry.block_table.shape[1] * entry.page_tokens
         K.latent_attention(q_abs, q_rot, entry.k_plane, self.rank, self.rot, H, ctx.positions, ctx.row_req, entry.block_table,
-                           entry.page_tokens, self.scale, lat, max_context=ctx.max_context)
+                           entry.page_tokens, self.scale, lat, max_context=reach)
         o = torch.empty((H * T, self.vdim), dtype=torch.float32, device=dev)
         K.tag = "value up"
         project(rt, lat, self.w_uv, o, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
         gated = torch.empty((T, H * self.vdim), dtype=rt.act_dtype, device=dev)
         K.tag = "head gate"
         K.latent_gate_out(o, proj, self.nq, H, self.vdim, gated)
-        K.tag = "o"
-        project(rt, gated, self.w_o, residual, accumulate=True)
-        K.tag = None
-        return None
+        return gated
+
+    def _plain_form(self, proj: torch.Tensor, ctx, entry) -> torch.Tensor:
+        rt = self.runtime
+        dev = proj.device
+        T, H = proj.shape[0], self.heads
+        layout = getattr(ctx, "_latent_tokens", None)
+        if layout is None:
+            # every token of the step's requests, cached and new, request after request (shared by the step's layers)
+            totals = [p + (ctx.h_req_start[i + 1] - ctx.h_req_start[i]) for i, p in enumerate(ctx.h_req_prior)]
+            base = np.zeros(ctx.n_requests, dtype=np.int32)
+            base[:len(totals)] = np.concatenate([[0], np.cumsum(totals)[:-1]])
+            tok_req = np.repeat(np.arange(len(totals), dtype=np.int32), totals)
+            tok_pos = np.concatenate([np.arange(t, dtype=np.int32) for t in totals])
+            host = torch.from_numpy(np.concatenate([base, tok_req, tok_pos]).astype(np.int32))
+            d = host.to(dev, non_blocking=False)
+            R, N = ctx.n_requests, int(tok_req.size)
+            layout = ctx._latent_tokens = (d[:R], d[R:R + N], d[R + N:], N)
+        req_base, tok_req, tok_pos, N = layout
+        plane = entry.k_plane
+        c_all = torch.empty((N, self.rank), dtype=torch.bfloat16, device=dev)
+        K.tag = "latent gather"
+        K.latent_gather(plane, self.rank, tok_req, tok_pos, entry.block_table, entry.page_tokens, c_all)
+        kp = torch.empty((N, H * self.dim), dtype=torch.bfloat16, device=dev)
+        vp = torch.empty((N, H * self.vdim), dtype=torch.bfloat16, device=dev)
+        K.tag = "key/value up"
+        project(rt, c_all, self.w_uk, kp)
+        project(rt, c_all, self.w_uv.view(H * self.vdim, self.rank), vp)
+        kx = torch.empty((N, H, self.dk_pad), dtype=torch.bfloat16, device=dev)
+        vx = torch.empty((N, H, self.dv_pad), dtype=torch.bfloat16, device=dev)
+        K.tag = "key/value pack"
+        K.latent_kv_pack(kp, vp, plane, self.rank, self.rot, tok_req, tok_pos, entry.block_table, entry.page_tokens, H, self.dim,
+                         self.vdim, kx, vx)
+        qx = torch.empty((T, H, self.dk_pad), dtype=torch.bfloat16, device=dev)
+        K.tag = "q split + rope"
+        K.latent_q_pack(proj, H, self.dim, self.rot, self.rotary, self.position.inv_freq, ctx.positions, qx)
+        ox = torch.empty((T, H, self.dv_pad), dtype=torch.bfloat16, device=dev)
+        K.tag = "attention"
+        K.latent_flash(qx, ox, kx, vx, ctx.req_start, ctx.req_prior, req_base, ctx.n_requests, H, self.scale)
+        gated = torch.empty((T, H * self.vdim), dtype=torch.bfloat16, device=dev)
+        K.tag = "head gate"
+        K.latent_gate_rows(ox, proj, self.nq, H, self.vdim, gated)
+        return gated

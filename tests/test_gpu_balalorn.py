@@ -362,3 +362,53 @@ def test_configurations_drawn_at_random(folders, seed):
             s = r.admit()
             check(feed(r, s, toks, cuts), want, dtype, f"{json.dumps(raw['layers'])} {dtype} cuts {cuts[:3]}")
             r.release(s)
+
+
+def test_portions_of_one_shape_replayed_from_graphs_at_growing_contexts(folders):
+    """bfloat16: a 400-token prompt in portions of 16 rows (the shape is captured at its second
+    appearance and replayed while the context grows far beyond what it was at capture), then
+    single tokens: every position against the plain implementation."""
+    d, (cfg, W) = folders("mixed", CONFIGS["mixed"], seed=7)
+    toks = helpers.random_tokens(cfg["vocab"], 420, seed=12)
+    want, _ = P.forward(toks, W, cfg)
+    r = runner_for(d, "bfloat16", max_tokens=448)
+    s = r.admit()
+    got = feed(r, s, toks, [16] * 25 + [1] * 20)
+    assert r.graph_replays > 20
+    check(got, want, "bfloat16", "portions of 16 from graphs")
+    e = rel_err(got, want)
+    assert float(e[300:].median()) < 2e-2, "late positions, whose keys lie beyond the capture-time context, drift"
+
+
+@pytest.mark.parametrize("name", ["mixed", "other", "wide"])
+def test_plain_form_of_latent_attention_for_long_portions(folders, name, monkeypatch):
+    """Steps with many rows build per-head keys and values and run the flash kernel; here the
+    threshold is lowered so that portions of 40 rows do, beside cached tokens of earlier
+    portions, and with three unequal requests in one step."""
+    from cajeta_llm_b200.engine.step import StepEntry
+    from cajeta_llm_b200.parts.latent_attention import LatentAttention
+    monkeypatch.setattr(LatentAttention, "EXPAND_MIN_ROWS", 8)
+    d, (cfg, W) = folders(name, CONFIGS[name], seed=7)
+    toks = [helpers.random_tokens(cfg["vocab"], n, seed=40 + n) for n in (150, 75, 33)]
+    want = [P.forward(t, W, cfg)[0] for t in toks]
+    r = runner_for(d, "bfloat16", max_tokens=192)
+    assert r.capture_max_rows == 7
+    s = r.admit()
+    check(feed(r, s, toks[0], [150]), want[0], "bfloat16", f"{name} whole prompt, plain form")
+    r.release(s)
+    s = r.admit()
+    check(feed(r, s, toks[0], [40, 70, 9, 31]), want[0], "bfloat16", f"{name} portions, plain form")
+    r.release(s)
+    slots = [r.admit() for _ in toks]
+    cuts = [(0, 70, 0, 40, 0, 20), (70, 150, 40, 75, 20, 33)]
+    got = [[], [], []]
+    for c in cuts:
+        entries = [StepEntry(slots[i], toks[i][c[2 * i]:c[2 * i + 1]], list(range(c[2 * i + 1] - c[2 * i]))) for i in range(3)]
+        out = r.step(entries).cpu()
+        at = 0
+        for i in range(3):
+            n = c[2 * i + 1] - c[2 * i]
+            got[i].append(out[at:at + n])
+            at += n
+    for i in range(3):
+        check(torch.cat(got[i]), want[i], "bfloat16", f"{name} request {i} of three in one step, plain form")
