@@ -57,8 +57,9 @@ def needs(design, s, rows, ctx, prefill):
         return out
     n_lat, n_ssd, n_delta = (L + 3) // 4 + L // 4, (L + 2) // 4, (L + 1) // 4
     width = s["rank"] + 64
+    # decode: the absorbed form reads each cache entry once; prompt portions: the plain form's flops
     out["attention"] = (rows * ctx * width * 2 * n_lat if not prefill else 0,
-                        2 * H * (width + s["rank"]) * rows * (rows + 1) // 2 * n_lat if prefill else 0)
+                        2 * H * (128 + 64 + 128) * rows * (rows + 1) // 2 * n_lat if prefill else 0)
     reqs = 1 if prefill else rows
     ssd_heads = 2 * s["width"] // 64
     state = n_ssd * ssd_heads * s["state"] * 64 * 4 + n_delta * H * 128 * 128 * 4

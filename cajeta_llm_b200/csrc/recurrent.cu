@@ -152,7 +152,11 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // A token's inputs (the two vectors over the state's rows, the block's columns of the value
 // vector, the two gate inputs) are staged in shared memory TOK tokens at a time, the next
 // TOK in flight (cp.async) while these are walked: a token's step then waits on shared
-// memory, not on a round trip to L2.  One staged token: [a: rows | b: rows | v: block's columns | 2].
+// memory, not on a round trip to L2.  One staged token: [a: rows | b: rows | v: block's columns | 4].
+// What does not depend on the state - the unit norms of q and k, softplus, the decay's
+// exponential, beta - is worked out for all staged tokens side by side (a warp a token)
+// before they are walked, so that the chain from one token's state to the next is only
+// decay, one sum over the rows, the update.
 template <int NPER, bool DELTA>
 __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) {
     cj::after_predecessor();
@@ -171,24 +175,28 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     const bool live = col < p.cols;
     const int rows = p.rows;
     const int group = head / (p.heads / p.groups);
-    const int stride = 2 * rows + cols_blk + 2;
+    const int tail = 2 * rows + cols_blk;                   // where a staged token's four scalars begin
+    const int stride = tail + 4;
     float* S = p.state + (size_t)slot * p.slot_stride + (size_t)head * rows * p.cols;
 
     auto stage = [&](int chunk, float* buf) {
         const int t0 = chunk * TOK, nt = min(TOK, n - t0);
-        for (int i = threadIdx.x; i < nt * stride; i += 128) {
-            const int tt = i / stride, e = i - tt * stride;
+        for (int tt = 0; tt < nt; ++tt) {
             const size_t row = (size_t)(first + t0 + tt);
-            const float* src = nullptr;
-            if (e < rows) src = p.x + row * p.ld + p.off_a + group * rows + e;
-            else if (e < 2 * rows) src = p.x + row * p.ld + p.off_b + group * rows + (e - rows);
-            else if (e < 2 * rows + cols_blk) {
-                const int c = col0 + e - 2 * rows;
-                if (c < p.cols) src = p.x + row * p.ld + p.off_v + head * p.cols + c;
-            } else if (e == 2 * rows + cols_blk) src = p.raw + row * p.ld_raw + p.off_dt + head;
-            else if (DELTA) src = p.raw + row * p.ld_raw + p.off_beta + head;
-            if (src) cp_async4(buf + i, src);
-            else buf[i] = 0.0f;
+            const float* xr = p.x + row * p.ld;
+            float* dst = buf + tt * stride;
+            for (int e = threadIdx.x; e < stride; e += 128) {
+                const float* src = nullptr;
+                if (e < rows) src = xr + p.off_a + group * rows + e;
+                else if (e < 2 * rows) src = xr + p.off_b + group * rows + (e - rows);
+                else if (e < tail) {
+                    const int c = col0 + e - 2 * rows;
+                    if (c < p.cols) src = xr + p.off_v + head * p.cols + c;
+                } else if (e == tail) src = p.raw + row * p.ld_raw + p.off_dt + head;
+                else if (DELTA && e == tail + 1) src = p.raw + row * p.ld_raw + p.off_beta + head;
+                if (src) cp_async4(dst + e, src);
+                else dst[e] = 0.0f;
+            }
         }
     };
 
@@ -211,11 +219,35 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
         cp_async_wait<1>();
         __syncthreads();
         const int nt = min(TOK, n - chunk * TOK);
+        // the staged tokens' scalars: a warp a token
+        for (int tt = warp; tt < nt; tt += 4) {
+            float* tk = cur + tt * stride;
+            if (DELTA) {
+                float qq = 0.0f, kk = 0.0f;
+                for (int d = lane; d < rows; d += 32) {
+                    qq = fmaf(tk[d], tk[d], qq);
+                    kk = fmaf(tk[rows + d], tk[rows + d], kk);
+                }
+                qq = warp_sum(qq);
+                kk = warp_sum(kk);
+                if (lane == 0) {
+                    const float g0 = tk[tail], g1 = tk[tail + 1];
+                    tk[tail] = expf(-A * softplus_f(g0 + bias));          // the decay
+                    tk[tail + 1] = sigmoid_f(g1);                         // beta
+                    tk[tail + 2] = p.q_scale / sqrtf(qq + 1e-6f);         // q becomes a unit vector times q_scale
+                    tk[tail + 3] = 1.0f / sqrtf(kk + 1e-6f);              // k a unit vector
+                }
+            } else if (lane == 0) {
+                const float dt = softplus_f(tk[tail] + bias);
+                tk[tail] = dt;
+                tk[tail + 1] = expf(-A * dt);
+            }
+        }
+        __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float* tk = cur + tt * stride;
             const int t = chunk * TOK + tt;
             const float xv = tk[2 * rows + lcol];
-            const float g0 = tk[2 * rows + cols_blk], g1 = tk[2 * rows + cols_blk + 1];
             float a[NPER], b[NPER];
 #pragma unroll
             for (int i = 0; i < NPER; ++i) {
@@ -224,21 +256,10 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
                 b[i] = d < rows ? tk[rows + d] : 0.0f;
             }
             if (DELTA) {
-                // a = q, b = k: unit vectors per head, q also times rows^(-1/2)
-                float qq = 0.0f, kk = 0.0f;
-#pragma unroll
-                for (int i = 0; i < NPER; ++i) { qq = fmaf(a[i], a[i], qq); kk = fmaf(b[i], b[i], kk); }
-                for (int o = cols_per_warp; o < 32; o <<= 1) {
-                    qq += __shfl_xor_sync(0xffffffffu, qq, o);
-                    kk += __shfl_xor_sync(0xffffffffu, kk, o);
-                }
-                const float qs = p.q_scale / sqrtf(qq + 1e-6f), ks = 1.0f / sqrtf(kk + 1e-6f);
-                const float decay = expf(-A * softplus_f(g0 + bias));
-                const float beta = sigmoid_f(g1);
+                const float decay = tk[tail], beta = tk[tail + 1], qs = tk[tail + 2], ks = tk[tail + 3];
                 float dot = 0.0f;
 #pragma unroll
                 for (int i = 0; i < NPER; ++i) {
-                    a[i] *= qs;
                     b[i] *= ks;
                     s[i] *= decay;
                     dot = fmaf(s[i], b[i], dot);
@@ -249,14 +270,13 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
 #pragma unroll
                 for (int i = 0; i < NPER; ++i) {
                     s[i] = fmaf(b[i], u, s[i]);
-                    y = fmaf(s[i], a[i], y);
+                    y = fmaf(s[i], a[i] * qs, y);
                 }
                 for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
                 if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = y;
             } else {
                 // a = B, b = C
-                const float dt = softplus_f(g0 + bias);
-                const float decay = expf(-A * dt);
+                const float dt = tk[tail], decay = tk[tail + 1];
                 const float dx = dt * xv;
                 float y = 0.0f;
 #pragma unroll
@@ -394,7 +414,7 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
     dim3 grid(requests, heads, (cols + cols_per_block - 1) / cols_per_block);
     if (grid.y > 65535 || grid.z > 65535) return CJ_ERR_SIZE;
     // tokens staged at a time: up to 16, as many as 96 KB of shared memory hold twice
-    const size_t token_bytes = (size_t)(2 * rows + cols_per_block + 2) * sizeof(float);
+    const size_t token_bytes = (size_t)(2 * rows + cols_per_block + 4) * sizeof(float);
     int TOK = (int)((96 * 1024) / (2 * token_bytes));
     if (TOK > 16) TOK = 16;
     if (TOK < 1) return CJ_ERR_SIZE;

@@ -167,8 +167,9 @@ def sub(weights, prefix):
     return {k[n:]: v for k, v in weights.items() if k.startswith(prefix + ".")}
 
 
-def forward(tokens, weights, config, positions=None):
-    """Logits [T, vocab] and the residual stream after every layer [layers, T, width]."""
+def forward(tokens, weights, config, positions=None, picks=None):
+    """Logits [T, vocab] and the residual stream after every layer [layers, T, width].
+    ``picks`` (a dict): receives, by layer index, the experts each position picked [T, top]."""
     eps = config["norm"]["eps"]
     T = len(tokens)
     positions = list(range(T)) if positions is None else positions
@@ -192,7 +193,9 @@ def forward(tokens, weights, config, positions=None):
             if ff["kind"] == "dense":
                 y = gated_ff(x, Wf["gate"], Wf["up"], Wf["down"])
             else:
-                y, _ = routed_ff(x, Wf, ff["router"]["experts"], ff["router"]["top"])
+                y, chosen = routed_ff(x, Wf, ff["router"]["experts"], ff["router"]["top"])
+                if picks is not None:
+                    picks[i] = chosen
             x = x + rms_unit(y, eps) * weights[f"l{i}.norm2"]
         after.append(x.clone())
     logits = (rms_unit(x, eps) * weights["final.norm"]) @ weights["head"].T
