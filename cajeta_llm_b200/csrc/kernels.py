@@ -395,12 +395,28 @@ def short_conv_commit(x: torch.Tensor, x_offset: int, channels: int, taps: int, 
 SCAN_SSD, SCAN_DELTA = 0, 1
 
 
+def state_scan_floats(heads: int, rows: int, cols: int) -> int:
+    """float32 entries of per-request state that ``state_scan`` needs for ``heads`` matrices of
+    rows x cols: the scan keeps them in the order its threads hold them (padded to whole tiles).
+    The same arithmetic as the kernel library's ``cj_state_scan_floats`` (tested equal)."""
+    dp = 4
+    while dp < 32 and dp < rows:
+        dp <<= 1
+    per = -(-rows // dp)
+    nper = 1
+    while nper < per:
+        nper <<= 1
+    cols_per_block = 4 * (32 // dp)
+    return heads * -(-cols // cols_per_block) * nper * 128
+
+
 def state_scan(mode: int, x: torch.Tensor, off_a: int, off_b: int, off_v: int, raw: torch.Tensor, off_dt: int, off_beta: int,
                A_log: torch.Tensor, dt_bias: torch.Tensor, skip: Optional[torch.Tensor], state: torch.Tensor, state_offset: int,
                req_start: torch.Tensor, req_slot: torch.Tensor, out: torch.Tensor, requests: int, heads: int, groups: int,
                rows: int, cols: int, q_scale: float = 1.0) -> None:
     """Walks every request's rows of the step in order through its recurrent state
-    (``state[slot, state_offset:]`` seen as [heads, rows, cols] float32) and writes a row's
+    (``state[slot, state_offset:]``, ``state_scan_floats(heads, rows, cols)`` float32 entries in the
+    scan's own layout; zero = the empty state) and writes a row's
     read-out to ``out`` [T, heads * cols].
 
     ``SCAN_SSD``: x columns off_a = B [groups, rows], off_b = C, off_v = x [heads, cols]; raw column
@@ -413,12 +429,12 @@ def state_scan(mode: int, x: torch.Tensor, off_a: int, off_b: int, off_v: int, r
     _need(req_start, "req_start", torch.int32), _need(req_slot, "req_slot", torch.int32)
     if skip is not None:
         _need(skip, "skip", torch.float32)
-    if state[0].numel() < state_offset + heads * rows * cols or out.shape[1] != heads * cols:
+    if state[0].numel() < state_offset + state_scan_floats(heads, rows, cols) or out.shape[1] != heads * cols:
         raise KernelError("state_scan: state or out too small")
     st = library("recurrent").cj_state_scan(
         _i(mode), _ptr(x), _i(x.stride(0)), _i(off_a), _i(off_b), _i(off_v), _ptr(raw), _i(raw.stride(0)), _i(off_dt), _i(off_beta),
         _ptr(A_log), _ptr(dt_bias), _ptr(skip), ctypes.c_void_p(state.data_ptr() + 4 * state_offset), _ll(state.stride(0)),
-        _ptr(req_start), _ptr(req_slot), _ptr(out), _i(requests), _i(heads), _i(groups), _i(rows), _i(cols), _f(q_scale), _stream())
+        _ll(state[0].numel() - state_offset), _ptr(req_start), _ptr(req_slot), _ptr(out), _i(requests), _i(heads), _i(groups), _i(rows), _i(cols), _f(q_scale), _stream())
     _check(st, "state_scan")
 
 

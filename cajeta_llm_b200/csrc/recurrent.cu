@@ -135,7 +135,7 @@ struct ScanArgs {
     int ld_raw;
     int off_dt, off_beta;      // ssd: dt ; delta: the decay's input a, beta's input b
     const float* A_log; const float* dt_bias; const float* skip;    // per head (skip: ssd's D)
-    float* state; long long slot_stride;     // per slot [heads][rows][cols] float32
+    float* state; long long slot_stride;     // per slot: the heads' matrices in the scan's own layout, float32
     const int* req_start; const int* req_slot;
     float* out;          // [T, heads * cols]
     int heads, groups, rows, cols;           // rows: state rows (N or key dim); cols: value dim
@@ -152,11 +152,23 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // A token's inputs (the two vectors over the state's rows, the block's columns of the value
 // vector, the two gate inputs) are staged in shared memory TOK tokens at a time, the next
 // TOK in flight (cp.async) while these are walked: a token's step then waits on shared
-// memory, not on a round trip to L2.  One staged token: [a: rows | b: rows | v: block's columns | 4].
+// memory, not on a round trip to L2.  One staged token: [a | b | v: block's columns | 4 scalars],
+// a and b laid out so that a lane's NPER rows (part + DP i) are contiguous: index part * NPER + i.
 // What does not depend on the state - the unit norms of q and k, softplus, the decay's
 // exponential, beta - is worked out for all staged tokens side by side (a warp a token)
 // before they are walked, so that the chain from one token's state to the next is only
-// decay, one sum over the rows, the update.
+// decay, one sum over the rows, the update.  The read-out's sum over the rows, which nothing
+// waits for, is carried along with the next token's sum (two independent butterflies side by side).
+//
+// The state of a (slot, head) is kept in the order the threads hold it: element
+// ((tile * NPER + i) * 128 + thread) is row part + DP i of column tile * cols_blk + lcol -
+// a layout that depends on the state's shape alone, read and written with full coalescing.
+// Nothing else reads the state (a slot is zeroed when it is admitted).
+__device__ __forceinline__ float lanes_sum(float v, int first) {
+    for (int o = first; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
 template <int NPER, bool DELTA>
 __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) {
     cj::after_predecessor();
@@ -173,11 +185,11 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     const int lcol = warp * cols_per_warp + (lane % cols_per_warp);
     const int col = col0 + lcol;
     const bool live = col < p.cols;
-    const int rows = p.rows;
+    const int rows = p.rows, padded = DP * NPER;            // rows rounded up to what the lanes hold
     const int group = head / (p.heads / p.groups);
-    const int tail = 2 * rows + cols_blk;                   // where a staged token's four scalars begin
+    const int tail = 2 * padded + cols_blk;                 // where a staged token's four scalars begin
     const int stride = tail + 4;
-    float* S = p.state + (size_t)slot * p.slot_stride + (size_t)head * rows * p.cols;
+    float* S = p.state + (size_t)slot * p.slot_stride + ((size_t)head * gridDim.z + blockIdx.z) * NPER * 128;
 
     auto stage = [&](int chunk, float* buf) {
         const int t0 = chunk * TOK, nt = min(TOK, n - t0);
@@ -187,10 +199,12 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
             float* dst = buf + tt * stride;
             for (int e = threadIdx.x; e < stride; e += 128) {
                 const float* src = nullptr;
-                if (e < rows) src = xr + p.off_a + group * rows + e;
-                else if (e < 2 * rows) src = xr + p.off_b + group * rows + (e - rows);
-                else if (e < tail) {
-                    const int c = col0 + e - 2 * rows;
+                if (e < 2 * padded) {
+                    const int v = e < padded ? e : e - padded;          // index part * NPER + i  ->  row part + DP i
+                    const int d = (v / NPER) + DP * (v % NPER);
+                    if (d < rows) src = xr + (e < padded ? p.off_a : p.off_b) + group * rows + d;
+                } else if (e < tail) {
+                    const int c = col0 + e - 2 * padded;
                     if (c < p.cols) src = xr + p.off_v + head * p.cols + c;
                 } else if (e == tail) src = p.raw + row * p.ld_raw + p.off_dt + head;
                 else if (DELTA && e == tail + 1) src = p.raw + row * p.ld_raw + p.off_beta + head;
@@ -205,13 +219,15 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     cp_async_commit();
     float s[NPER];
 #pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-        const int d = part + DP * i;
-        s[i] = (live && d < rows) ? S[(size_t)d * p.cols + col] : 0.0f;
-    }
+    for (int i = 0; i < NPER; ++i) s[i] = S[i * 128 + threadIdx.x];
     const float A = expf(p.A_log[head]);
     const float bias = p.dt_bias[head];
     const float skip = DELTA ? 0.0f : p.skip[head];
+    float* out = p.out + (size_t)first * p.heads * p.cols + head * p.cols + col;
+    const size_t out_ld = (size_t)p.heads * p.cols;
+    const bool writer = live && part == 0;
+    float y_prev = 0.0f;                                    // the token before's read-out, its sum over the lanes still owed
+    int t_prev = -1;
     for (int chunk = 0; chunk < chunks; ++chunk) {
         float* cur = staged + (chunk & 1) * TOK * stride;
         if (chunk + 1 < chunks) stage(chunk + 1, staged + ((chunk + 1) & 1) * TOK * stride);
@@ -224,9 +240,9 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
             float* tk = cur + tt * stride;
             if (DELTA) {
                 float qq = 0.0f, kk = 0.0f;
-                for (int d = lane; d < rows; d += 32) {
+                for (int d = lane; d < padded; d += 32) {
                     qq = fmaf(tk[d], tk[d], qq);
-                    kk = fmaf(tk[rows + d], tk[rows + d], kk);
+                    kk = fmaf(tk[padded + d], tk[padded + d], kk);
                 }
                 qq = warp_sum(qq);
                 kk = warp_sum(kk);
@@ -246,14 +262,22 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float* tk = cur + tt * stride;
-            const int t = chunk * TOK + tt;
-            const float xv = tk[2 * rows + lcol];
+            const float xv = tk[2 * padded + lcol];
             float a[NPER], b[NPER];
+            if (NPER % 4 == 0) {
 #pragma unroll
-            for (int i = 0; i < NPER; ++i) {
-                const int d = part + DP * i;
-                a[i] = d < rows ? tk[d] : 0.0f;
-                b[i] = d < rows ? tk[rows + d] : 0.0f;
+                for (int i = 0; i < NPER; i += 4) {
+                    const float4 va = *(const float4*)(tk + part * NPER + i);
+                    const float4 vb = *(const float4*)(tk + padded + part * NPER + i);
+                    a[i] = va.x; a[i + 1] = va.y; a[i + 2] = va.z; a[i + 3] = va.w;
+                    b[i] = vb.x; b[i + 1] = vb.y; b[i + 2] = vb.z; b[i + 3] = vb.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    a[i] = tk[part * NPER + i];
+                    b[i] = tk[padded + part * NPER + i];
+                }
             }
             if (DELTA) {
                 const float decay = tk[tail], beta = tk[tail + 1], qs = tk[tail + 2], ks = tk[tail + 3];
@@ -264,7 +288,12 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
                     s[i] *= decay;
                     dot = fmaf(s[i], b[i], dot);
                 }
-                for (int o = cols_per_warp; o < 32; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                // this token's S^T k and the token before's read-out: two sums over the lanes, side by side
+                for (int o = cols_per_warp; o < 32; o <<= 1) {
+                    dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    y_prev += __shfl_xor_sync(0xffffffffu, y_prev, o);
+                }
+                if (writer && t_prev >= 0) out[(size_t)t_prev * out_ld] = y_prev;
                 const float u = beta * (xv - dot);
                 float y = 0.0f;
 #pragma unroll
@@ -272,8 +301,8 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
                     s[i] = fmaf(b[i], u, s[i]);
                     y = fmaf(s[i], a[i] * qs, y);
                 }
-                for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-                if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = y;
+                y_prev = y;
+                t_prev = chunk * TOK + tt;
             } else {
                 // a = B, b = C
                 const float dt = tk[tail], decay = tk[tail + 1];
@@ -284,17 +313,18 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
                     s[i] = fmaf(decay, s[i], a[i] * dx);
                     y = fmaf(s[i], b[i], y);
                 }
-                for (int o = cols_per_warp; o < 32; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-                if (live && part == 0) p.out[(size_t)(first + t) * p.heads * p.cols + head * p.cols + col] = fmaf(skip, xv, y);
+                y = lanes_sum(y, cols_per_warp);
+                if (writer) out[(size_t)(chunk * TOK + tt) * out_ld] = fmaf(skip, xv, y);
             }
         }
         __syncthreads();                       // everyone has walked this buffer before it is staged into again
     }
-#pragma unroll
-    for (int i = 0; i < NPER; ++i) {
-        const int d = part + DP * i;
-        if (live && d < rows) S[(size_t)d * p.cols + col] = s[i];
+    if (DELTA) {
+        y_prev = lanes_sum(y_prev, cols_per_warp);
+        if (writer && t_prev >= 0) out[(size_t)t_prev * out_ld] = y_prev;
     }
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) S[i * 128 + threadIdx.x] = s[i];
 }
 
 // ---------------------------------------------------------------------------------
@@ -397,24 +427,28 @@ CJ_EXPORT int cj_short_conv_commit(const float* in, int ld_in, int C, int taps, 
 // mode 1: the gated delta rule (off_a = q, off_b = k, off_v = v; off_dt = decay input, off_beta in raw).
 CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off_b, int off_v, const float* raw, int ld_raw,
                             int off_dt, int off_beta, const float* A_log, const float* dt_bias, const float* skip, float* state,
-                            long long slot_stride, const int* req_start, const int* req_slot, float* out, int requests,
-                            int heads, int groups, int rows, int cols, float q_scale, cudaStream_t stream) {
+                            long long slot_stride, long long state_floats, const int* req_start, const int* req_slot, float* out,
+                            int requests, int heads, int groups, int rows, int cols, float q_scale, cudaStream_t stream) {
     if (requests <= 0) return 0;
     if (!x || !raw || !A_log || !dt_bias || !state || !req_start || !req_slot || !out) return CJ_ERR_ARG;
     if (mode == 0 && !skip) return CJ_ERR_ARG;
     if (heads <= 0 || groups <= 0 || heads % groups != 0 || rows <= 0 || cols <= 0) return CJ_ERR_SIZE;
-    // a column's rows are dealt to DP lanes: about 8 rows a lane where 32 lanes allow it, at most 64
+    // a column's rows are dealt to as many lanes as there are rows, up to a whole warp: the walk over a
+    // request's tokens is a chain of latencies, and more, lighter threads shorten it
     int DP = 4;
-    while (DP < 32 && (rows + DP - 1) / DP > 8) DP <<= 1;
+    while (DP < 32 && DP < rows) DP <<= 1;
     const int per = (rows + DP - 1) / DP;
     if (per > 64) return CJ_ERR_SIZE;
+    int nper = 1;
+    while (nper < per) nper <<= 1;
     ScanArgs p{x, ld, off_a, off_b, off_v, raw, ld_raw, off_dt, off_beta, A_log, dt_bias, skip, state, slot_stride,
                req_start, req_slot, out, heads, groups, rows, cols, q_scale};
     const int cols_per_block = 4 * (32 / DP);
     dim3 grid(requests, heads, (cols + cols_per_block - 1) / cols_per_block);
     if (grid.y > 65535 || grid.z > 65535) return CJ_ERR_SIZE;
+    if (state_floats < (long long)heads * grid.z * nper * 128) return CJ_ERR_SIZE;
     // tokens staged at a time: up to 16, as many as 96 KB of shared memory hold twice
-    const size_t token_bytes = (size_t)(2 * rows + cols_per_block + 4) * sizeof(float);
+    const size_t token_bytes = (size_t)(2 * DP * nper + cols_per_block + 4) * sizeof(float);
     int TOK = (int)((96 * 1024) / (2 * token_bytes));
     if (TOK > 16) TOK = 16;
     if (TOK < 1) return CJ_ERR_SIZE;
@@ -430,12 +464,29 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
         if (mode == 0) cj::launch(scan_kernel<N, false>, grid, dim3(128), smem, stream, p, DP, TOK);                    \
         else cj::launch(scan_kernel<N, true>, grid, dim3(128), smem, stream, p, DP, TOK);                               \
     } while (0)
-    if (per <= 8) LAUNCH(8);
-    else if (per <= 16) LAUNCH(16);
-    else if (per <= 32) LAUNCH(32);
-    else LAUNCH(64);
+    switch (nper) {
+        case 1: LAUNCH(1); break;
+        case 2: LAUNCH(2); break;
+        case 4: LAUNCH(4); break;
+        case 8: LAUNCH(8); break;
+        case 16: LAUNCH(16); break;
+        case 32: LAUNCH(32); break;
+        default: LAUNCH(64);
+    }
 #undef LAUNCH
     return launch_status();
+}
+
+// floats of state one (slot, schedule entry) needs for heads matrices of rows x cols in the scan's own layout
+CJ_EXPORT long long cj_state_scan_floats(int heads, int rows, int cols) {
+    if (heads <= 0 || rows <= 0 || cols <= 0) return 0;
+    int DP = 4;
+    while (DP < 32 && DP < rows) DP <<= 1;
+    const int per = (rows + DP - 1) / DP;
+    int nper = 1;
+    while (nper < per) nper <<= 1;
+    const int cols_per_block = 4 * (32 / DP);
+    return (long long)heads * ((cols + cols_per_block - 1) / cols_per_block) * nper * 128;
 }
 
 CJ_EXPORT int cj_gated_group_norm(const float* y, int n, int part_len, const float* z, int ld_z, const float* w, int w_len,

@@ -5,7 +5,8 @@ Both project the row, pass part of the projection through a short causal convolu
 time (per channel, ``conv`` taps, then SiLU) and walk the request's tokens in order through a
 float32 state ``S`` per head.  The state of a request lives in its slot of the cache
 manager's state tensor (one flat float32 vector per schedule entry: the convolution's last
-``conv - 1`` inputs, then the heads' ``S``); it is zeroed when the slot is admitted.  Both
+``conv - 1`` inputs, then the heads' ``S`` in the order the scan's threads hold them); it is
+zeroed when the slot is admitted.  Both
 find their rows, requests and slots in the step's device metadata only, so their steps can
 be captured into CUDA graphs (``graph_safe``).
 
@@ -94,7 +95,7 @@ class StateSpaceMixer(_StateMixer):
         self.w_in = self.w_conv = self.b_conv = self.dt_bias = self.A_log = self.D = self.w_norm = self.w_o = None
 
     def state_need(self) -> Optional[StateNeed]:
-        return StateNeed((self.conv_state + self.heads * self.n_state * self.vdim,), torch.float32)
+        return StateNeed((self.conv_state + K.state_scan_floats(self.heads, self.n_state, self.vdim),), torch.float32)
 
     def params(self) -> Dict[str, ParamSpec]:
         return {
@@ -160,7 +161,7 @@ class GatedDeltaMixer(_StateMixer):
         self.w_in = self.w_conv = self.dt_bias = self.A_log = self.w_norm = self.w_o = None
 
     def state_need(self) -> Optional[StateNeed]:
-        return StateNeed((self.conv_state + self.heads * self.dim * self.vdim,), torch.float32)
+        return StateNeed((self.conv_state + K.state_scan_floats(self.heads, self.dim, self.vdim),), torch.float32)
 
     def params(self) -> Dict[str, ParamSpec]:
         p = {}

@@ -57,7 +57,9 @@ def test_tensor_names_and_shapes():
     assert p["l3.mix.q"] == (12, 32) and p["l3.mix.v.conv"] == (20, 2) and p["l3.mix.a"] == (4, 32) and p["l3.mix.norm"] == (5,)
     needs, states = model.kv_needs(), model.state_needs()
     assert needs[0].head_dim == 14 and needs[0].kv_heads == 1 and not needs[0].values and needs[1] is None
-    assert states[1].shape == (2 * 44 + 4 * 5 * 6,) and states[3].shape == (1 * 44 + 4 * 6 * 5,) and states[0] is None
+    from cajeta_llm_b200.csrc.kernels import state_scan_floats
+    assert states[1].shape == (2 * 44 + state_scan_floats(4, 5, 6),) and states[3].shape == (1 * 44 + state_scan_floats(4, 6, 5),)
+    assert states[0] is None and state_scan_floats(4, 5, 6) >= 4 * 5 * 6 and state_scan_floats(16, 128, 128) == 16 * 128 * 128
 
 
 @pytest.mark.parametrize("change, message", [

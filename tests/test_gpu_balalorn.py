@@ -445,3 +445,12 @@ def test_plain_form_of_latent_attention_for_long_portions(folders, name, monkeyp
             at += n
     for i in range(3):
         check(torch.cat(got[i]), want[i], "bfloat16", f"{name} request {i} of three in one step, plain form")
+
+
+def test_state_sizes_agree_between_the_host_and_the_kernel_library():
+    import ctypes
+    from cajeta_llm_b200.csrc import kernels as K
+    fn = K.library("recurrent").cj_state_scan_floats
+    fn.restype = ctypes.c_longlong
+    for heads, rows, cols in [(1, 1, 1), (4, 5, 6), (6, 48, 48), (3, 12, 70), (16, 128, 128), (64, 128, 64), (2, 300, 33), (1, 2048, 8)]:
+        assert fn(heads, rows, cols) == K.state_scan_floats(heads, rows, cols) >= heads * rows * cols
