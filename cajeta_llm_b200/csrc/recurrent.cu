@@ -165,6 +165,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // a layout that depends on the state's shape alone, read and written with full coalescing.
 // Nothing else reads the state (a slot is zeroed when it is admitted).
 __device__ __forceinline__ float lanes_sum(float v, int first) {
+    if (first == 1) return warp_sum(v);                     // a column's rows span the whole warp: unrolled
     for (int o = first; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
@@ -191,24 +192,51 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
     const int stride = tail + 4;
     float* S = p.state + (size_t)slot * p.slot_stride + ((size_t)head * gridDim.z + blockIdx.z) * NPER * 128;
 
+    // Where a staged token's entries come from is the same for every token: a thread works out, once,
+    // the source of the entries it copies (entry e = thread + 128 k) as an offset into the token's row
+    // of x (kind 1) or of raw (kind 2), or nothing (kind 0: padding, written as zero).
+    constexpr int OWN = 4;                                  // entries a thread remembers; longer tokens take the general loop
+    int own_off[OWN], own_kind[OWN];
+    auto source = [&](int e, int& off) -> int {
+        if (e < 2 * padded) {
+            const int v = e < padded ? e : e - padded;      // index part * NPER + i  ->  row part + DP i
+            const int d = (v / NPER) + DP * (v % NPER);
+            off = (e < padded ? p.off_a : p.off_b) + group * rows + d;
+            return d < rows ? 1 : 0;
+        }
+        if (e < tail) {
+            const int c = col0 + e - 2 * padded;
+            off = p.off_v + head * p.cols + c;
+            return c < p.cols ? 1 : 0;
+        }
+        if (e == tail) { off = p.off_dt + head; return 2; }
+        if (DELTA && e == tail + 1) { off = p.off_beta + head; return 2; }
+        off = 0;
+        return 0;
+    };
+#pragma unroll
+    for (int k = 0; k < OWN; ++k) {
+        const int e = threadIdx.x + 128 * k;
+        own_kind[k] = e < stride ? source(e, own_off[k]) : -1;
+        if (e >= stride) own_off[k] = 0;
+    }
     auto stage = [&](int chunk, float* buf) {
         const int t0 = chunk * TOK, nt = min(TOK, n - t0);
         for (int tt = 0; tt < nt; ++tt) {
             const size_t row = (size_t)(first + t0 + tt);
             const float* xr = p.x + row * p.ld;
+            const float* rr = p.raw + row * p.ld_raw;
             float* dst = buf + tt * stride;
-            for (int e = threadIdx.x; e < stride; e += 128) {
-                const float* src = nullptr;
-                if (e < 2 * padded) {
-                    const int v = e < padded ? e : e - padded;          // index part * NPER + i  ->  row part + DP i
-                    const int d = (v / NPER) + DP * (v % NPER);
-                    if (d < rows) src = xr + (e < padded ? p.off_a : p.off_b) + group * rows + d;
-                } else if (e < tail) {
-                    const int c = col0 + e - 2 * padded;
-                    if (c < p.cols) src = xr + p.off_v + head * p.cols + c;
-                } else if (e == tail) src = p.raw + row * p.ld_raw + p.off_dt + head;
-                else if (DELTA && e == tail + 1) src = p.raw + row * p.ld_raw + p.off_beta + head;
-                if (src) cp_async4(dst + e, src);
+#pragma unroll
+            for (int k = 0; k < OWN; ++k) {
+                const int e = threadIdx.x + 128 * k;
+                if (own_kind[k] > 0) cp_async4(dst + e, (own_kind[k] == 1 ? xr : rr) + own_off[k]);
+                else if (own_kind[k] == 0) dst[e] = 0.0f;
+            }
+            for (int e = threadIdx.x + 128 * OWN; e < stride; e += 128) {
+                int off;
+                const int kind = source(e, off);
+                if (kind > 0) cp_async4(dst + e, (kind == 1 ? xr : rr) + off);
                 else dst[e] = 0.0f;
             }
         }
@@ -289,9 +317,17 @@ __global__ void __launch_bounds__(128) scan_kernel(ScanArgs p, int DP, int TOK) 
                     dot = fmaf(s[i], b[i], dot);
                 }
                 // this token's S^T k and the token before's read-out: two sums over the lanes, side by side
-                for (int o = cols_per_warp; o < 32; o <<= 1) {
-                    dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                    y_prev += __shfl_xor_sync(0xffffffffu, y_prev, o);
+                if (cols_per_warp == 1) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                        y_prev += __shfl_xor_sync(0xffffffffu, y_prev, o);
+                    }
+                } else {
+                    for (int o = cols_per_warp; o < 32; o <<= 1) {
+                        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                        y_prev += __shfl_xor_sync(0xffffffffu, y_prev, o);
+                    }
                 }
                 if (writer && t_prev >= 0) out[(size_t)t_prev * out_ld] = y_prev;
                 const float u = beta * (xv - dot);
