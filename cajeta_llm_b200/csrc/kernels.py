@@ -483,7 +483,7 @@ def latent_q_split(q: torch.Tensor, heads: int, dim: int, rot: int, rotary: int,
     _check(st, "latent_q_split")
 
 
-LATENT_SPLIT_MIN_KEYS = 128      # a stretch of a row's keys is at least this long
+LATENT_SPLIT_MIN_KEYS = 64       # a stretch of a row's keys is at least this long
 LATENT_FILL_BLOCKS = 592         # blocks that fill the machine (four an SM); fewer: the rows' keys are cut into stretches
 
 

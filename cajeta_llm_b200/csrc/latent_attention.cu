@@ -140,20 +140,38 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(
     for (int k0 = key_begin; k0 < key_end; k0 += LA_KEYS) {
         const int n_keys = min(LA_KEYS, key_end - k0);
         __syncthreads();                                        // the chunk before has been used up (and qs is written)
-        // bring the chunk in: a key's entry is contiguous in its page
-        if ((width * sizeof(TC)) % 4 == 0) {
-            const int words = width * (int)sizeof(TC) / 4;
-            for (int j = warp; j < n_keys; j += LA_HEADS) {
-                const int kp = k0 + j;
-                const uint32_t* src = (const uint32_t*)(plane + ((size_t)pages[kp / page_tokens] * page_tokens + kp % page_tokens) * width);
-                for (int e = lane; e < words; e += 32) ks[j * row_words + e] = src[e];
+        // bring the chunk in: a key's entry is contiguous in its page.  A warp brings four keys
+        // (warp, warp + 8, ...), their loads side by side: four independent round trips in flight
+        // a pass instead of one.
+        {
+            constexpr int PER_WARP = LA_KEYS / LA_HEADS;
+            const TC* srcs[PER_WARP];
+#pragma unroll
+            for (int u = 0; u < PER_WARP; ++u) {
+                const int j = warp + LA_HEADS * u;
+                const int kp = k0 + (j < n_keys ? j : 0);
+                srcs[u] = plane + ((size_t)pages[kp / page_tokens] * page_tokens + kp % page_tokens) * width;
             }
-        } else {
-            TC* kd = (TC*)ks;
-            for (int j = warp; j < n_keys; j += LA_HEADS) {
-                const int kp = k0 + j;
-                const TC* src = plane + ((size_t)pages[kp / page_tokens] * page_tokens + kp % page_tokens) * width;
-                for (int e = lane; e < width; e += 32) kd[j * row_elems + e] = src[e];
+            if ((width * sizeof(TC)) % 4 == 0) {
+                const int words = width * (int)sizeof(TC) / 4;
+                for (int e = lane; e < words; e += 32) {
+                    uint32_t v[PER_WARP];
+#pragma unroll
+                    for (int u = 0; u < PER_WARP; ++u) v[u] = warp + LA_HEADS * u < n_keys ? ((const uint32_t*)srcs[u])[e] : 0u;
+#pragma unroll
+                    for (int u = 0; u < PER_WARP; ++u)
+                        if (warp + LA_HEADS * u < n_keys) ks[(warp + LA_HEADS * u) * row_words + e] = v[u];
+                }
+            } else {
+                TC* kd = (TC*)ks;
+                for (int e = lane; e < width; e += 32) {
+                    TC v[PER_WARP];
+#pragma unroll
+                    for (int u = 0; u < PER_WARP; ++u) v[u] = warp + LA_HEADS * u < n_keys ? srcs[u][e] : from_f32<TC>(0.0f);
+#pragma unroll
+                    for (int u = 0; u < PER_WARP; ++u)
+                        if (warp + LA_HEADS * u < n_keys) kd[(warp + LA_HEADS * u) * row_elems + e] = v[u];
+                }
             }
         }
         __syncthreads();
