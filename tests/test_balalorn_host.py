@@ -160,3 +160,16 @@ def test_routed_feed_forward_weights_the_input():
         assert picks[t].tolist() == top
         want = sum(P.gated_ff(s[t, e] * h[t:t + 1], W[f"e{e}.gate"], W[f"e{e}.up"], W[f"e{e}.down"])[0] for e in top)
         assert torch.allclose(out[t], want, atol=1e-12)
+
+
+def test_command_line_writes_a_random_model_folder(tmp_path):
+    import subprocess
+    import sys
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(RAW))
+    out = tmp_path / "model"
+    r = subprocess.run([sys.executable, "-m", "cajeta_llm_b200", "random-weights", "--config", str(cfg), "--seed", "4", "--out", str(out)],
+                       cwd=helpers.ROOT, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-1000:]
+    config, W = P.read_model(str(out))
+    assert config["architecture"] == "Balalorn" and config["layers"] == RAW["layers"] and W["head"].shape == (50, 32)
