@@ -400,7 +400,9 @@ def state_scan_floats(heads: int, rows: int, cols: int) -> int:
     rows x cols: the scan keeps them in the order its threads hold them (padded to whole tiles).
     The same arithmetic as the kernel library's ``cj_state_scan_floats`` (tested equal)."""
     dp = 4
-    while dp < 32 and dp < rows:
+    while dp < 32 and dp < rows and (dp < 8 or heads * cols * dp // 32 < 592):
+        dp <<= 1
+    while dp < 32 and -(-rows // dp) > 64:
         dp <<= 1
     per = -(-rows // dp)
     nper = 1

@@ -403,6 +403,21 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int n, int 
 
 }  // namespace
 
+// Lanes a column's rows are dealt to (4, 8, 16 or 32).  Every (column, token) costs a warp its staging,
+// its butterflies and its store whatever the lanes hold, so fewer lanes a column - more columns a
+// warp - mean fewer instructions in all; but one request's scan is a chain, and with too few warps
+// the chain's latencies lie bare.  So: the fewest lanes (at least 8 where there are 8 rows) that
+// still give ONE request's scan a warp for each of a B200's 592 warp schedulers; and few enough rows
+// a lane (64) to stay in registers.  Measured on two scans of a 2,048-token prompt, 8 / 16 / 32 lanes:
+// 32 + 8 heads 2.40 / 2.46 / 2.36 ms (all short of warps), 64 + 16 heads 2.63 / 2.85 / 3.64 ms.
+// The state's layout follows from this number, so it depends on the state's shape alone.
+static int scan_lanes(int heads, int rows, int cols) {
+    int dp = 4;
+    while (dp < 32 && dp < rows && (dp < 8 || (long long)heads * cols * dp / 32 < 592)) dp <<= 1;
+    while (dp < 32 && (rows + dp - 1) / dp > 64) dp <<= 1;
+    return dp;
+}
+
 CJ_EXPORT int cj_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (!x || !out) return CJ_ERR_ARG;
@@ -469,10 +484,7 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
     if (!x || !raw || !A_log || !dt_bias || !state || !req_start || !req_slot || !out) return CJ_ERR_ARG;
     if (mode == 0 && !skip) return CJ_ERR_ARG;
     if (heads <= 0 || groups <= 0 || heads % groups != 0 || rows <= 0 || cols <= 0) return CJ_ERR_SIZE;
-    // a column's rows are dealt to as many lanes as there are rows, up to a whole warp: the walk over a
-    // request's tokens is a chain of latencies, and more, lighter threads shorten it
-    int DP = 4;
-    while (DP < 32 && DP < rows) DP <<= 1;
+    const int DP = scan_lanes(heads, rows, cols);
     const int per = (rows + DP - 1) / DP;
     if (per > 64) return CJ_ERR_SIZE;
     int nper = 1;
@@ -516,8 +528,7 @@ CJ_EXPORT int cj_state_scan(int mode, const float* x, int ld, int off_a, int off
 // floats of state one (slot, schedule entry) needs for heads matrices of rows x cols in the scan's own layout
 CJ_EXPORT long long cj_state_scan_floats(int heads, int rows, int cols) {
     if (heads <= 0 || rows <= 0 || cols <= 0) return 0;
-    int DP = 4;
-    while (DP < 32 && DP < rows) DP <<= 1;
+    const int DP = scan_lanes(heads, rows, cols);
     const int per = (rows + DP - 1) / DP;
     int nper = 1;
     while (nper < per) nper <<= 1;

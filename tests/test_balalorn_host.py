@@ -59,7 +59,7 @@ def test_tensor_names_and_shapes():
     assert needs[0].head_dim == 14 and needs[0].kv_heads == 1 and not needs[0].values and needs[1] is None
     from cajeta_llm_b200.csrc.kernels import state_scan_floats
     assert states[1].shape == (2 * 44 + state_scan_floats(4, 5, 6),) and states[3].shape == (1 * 44 + state_scan_floats(4, 6, 5),)
-    assert states[0] is None and state_scan_floats(4, 5, 6) >= 4 * 5 * 6 and state_scan_floats(16, 128, 128) == 16 * 128 * 128
+    assert states[0] is None and state_scan_floats(4, 5, 6) >= 4 * 5 * 6 and state_scan_floats(16, 128, 128) == 16 * 128 * 128 == state_scan_floats(64, 128, 32)
 
 
 @pytest.mark.parametrize("change, message", [

@@ -452,5 +452,6 @@ def test_state_sizes_agree_between_the_host_and_the_kernel_library():
     from cajeta_llm_b200.csrc import kernels as K
     fn = K.library("recurrent").cj_state_scan_floats
     fn.restype = ctypes.c_longlong
-    for heads, rows, cols in [(1, 1, 1), (4, 5, 6), (6, 48, 48), (3, 12, 70), (16, 128, 128), (64, 128, 64), (2, 300, 33), (1, 2048, 8)]:
+    for heads, rows, cols in [(1, 1, 1), (4, 5, 6), (6, 48, 48), (3, 12, 70), (16, 128, 128), (64, 128, 64), (2, 300, 33), (1, 2048, 8),
+                              (128, 128, 64), (8, 128, 128), (32, 64, 64), (512, 16, 64), (40, 2048, 256)]:
         assert fn(heads, rows, cols) == K.state_scan_floats(heads, rows, cols) >= heads * rows * cols
