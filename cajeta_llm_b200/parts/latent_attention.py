@@ -3,7 +3,7 @@
 Per row at position p, H heads with ``dim`` unrotated and ``rot_dim`` rotated query/key
 entries, values of ``vdim``, latent of ``kv_rank``::
 
-    q = W_q x                       laid out head by head as [dim | rot_dim]
+    q = W_q x                       each head: [dim plain entries | rot_dim entries to rotate]
     d = W_dkv x                     kv_rank + rot_dim rows
     c = rms(d[:kv_rank]) * w        the latent           } one cache entry
     r = rotate(d[kv_rank:], p)      the shared key part  } of kv_rank + rot_dim
