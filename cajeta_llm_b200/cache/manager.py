@@ -29,13 +29,16 @@ from .pages import CacheBooks, CacheError, GroupSpec
 class CacheManager:
     def __init__(self, kv_needs: Sequence[Optional[KvNeed]], state_needs: Sequence[Optional[StateNeed]],
                  cache_from: Sequence[Optional[int]], page_tokens: int, max_seqs: int, max_tokens_per_seq: int,
-                 num_pages, cache_dtype: torch.dtype, device: torch.device | str | None):
+                 num_pages, cache_dtype: torch.dtype, device: torch.device | str | None,
+                 named_state_needs: Optional[Dict[str, StateNeed]] = None):
         """``kv_needs[i]`` / ``state_needs[i]`` belong to schedule entry ``i``;
         ``cache_from[i]`` names the entry whose plane entry ``i`` reads instead of owning
         one.  ``num_pages`` is the pool size of every group, or a function
         ``GroupSpec -> pages`` that sizes each group by its own need (a windowed group holds
         far fewer pages a request than one that keeps every key).  ``device=None`` keeps only
-        the books (no tensors), for tests of the bookkeeping."""
+        the books (no tensors), for tests of the bookkeeping.  ``named_state_needs``: per-request state
+        of parts that are not schedule entries (an embedding that remembers a request's last token),
+        by name; found under that name in ``state`` and zeroed at admission like the entries'."""
         n = len(kv_needs)
         self.page_tokens = page_tokens
         self.max_seqs = max_seqs
@@ -49,7 +52,7 @@ class CacheManager:
             need = kv_needs[i]
             if need is None or cache_from[i] is not None:
                 continue
-            spec = GroupSpec(need.kv_heads, need.head_dim, need.window, getattr(need, "values", True))
+            spec = GroupSpec(need.kv_heads, need.head_dim, need.window, getattr(need, "values", True), getattr(need, "value_dim", 0))
             if spec not in specs:
                 specs.append(spec)
                 plane_count.append(0)
@@ -64,7 +67,8 @@ class CacheManager:
             if self.entry_group[src] is None:
                 raise CacheError(f"schedule entry {i} reads the cache of entry {src}, which caches nothing")
             a, b = kv_needs[i], kv_needs[src]
-            if a is None or (a.kv_heads, a.head_dim, getattr(a, "values", True)) != (b.kv_heads, b.head_dim, getattr(b, "values", True)):
+            if a is None or (a.kv_heads, a.head_dim, getattr(a, "values", True), getattr(a, "value_dim", 0)) != (
+                    b.kv_heads, b.head_dim, getattr(b, "values", True), getattr(b, "value_dim", 0)):
                 raise CacheError(f"schedule entry {i} cannot read the cache of entry {src}: head layout differs")
             if b.window > 0 and (a.window == 0 or a.window > b.window):
                 raise CacheError(f"schedule entry {i} (window {a.window}) cannot read the cache of entry {src}, "
@@ -77,15 +81,18 @@ class CacheManager:
         self.books = CacheBooks(specs, counts, page_tokens, max_seqs, max_tokens_per_seq)
         self.k: List[torch.Tensor] = []
         self.v: List[Optional[torch.Tensor]] = []      # None for a group that keeps no values
-        self.state: Dict[int, torch.Tensor] = {}
+        self.state: Dict[object, torch.Tensor] = {}      # by schedule entry (int) or by name (str)
         if self.device is not None:
             for spec, planes, pages in zip(specs, plane_count, counts):
                 shape = (planes, pages, spec.kv_heads, page_tokens, spec.head_dim)
                 self.k.append(torch.zeros(shape, dtype=cache_dtype, device=self.device))
-                self.v.append(torch.zeros(shape, dtype=cache_dtype, device=self.device) if spec.values else None)
+                v_shape = shape[:-1] + (spec.value_dim or spec.head_dim,)
+                self.v.append(torch.zeros(v_shape, dtype=cache_dtype, device=self.device) if spec.values else None)
             for i, need in enumerate(state_needs):
                 if need is not None:
                     self.state[i] = torch.zeros((max_seqs,) + tuple(need.shape), dtype=need.dtype, device=self.device)
+            for name, need in (named_state_needs or {}).items():
+                self.state[name] = torch.zeros((max_seqs,) + tuple(need.shape), dtype=need.dtype, device=self.device)
 
     # -- requests --------------------------------------------------------------------
     def admit(self) -> Optional[int]:
@@ -145,7 +152,7 @@ class CacheManager:
         for g, spec in enumerate(self.group_specs):
             planes = sum(1 for e, gg in enumerate(self.entry_group) if gg == g and self.entry_plane[e] is not None
                          and self._owns(e))
-            total += (2 if spec.values else 1) * planes * spec.kv_heads * spec.head_dim * size
+            total += planes * spec.kv_heads * (spec.head_dim + ((spec.value_dim or spec.head_dim) if spec.values else 0)) * size
         return total
 
     def _owns(self, entry: int) -> bool:

@@ -146,6 +146,7 @@ class GroupSpec:
     head_dim: int
     window: int      # 0: every key is kept
     values: bool = True      # False: one vector per token and head, no plane of values
+    value_dim: int = 0       # the values' head size when it is not head_dim
 
 
 class _GroupPages:

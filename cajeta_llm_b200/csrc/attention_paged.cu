@@ -2,6 +2,9 @@
 // from cache pages through the request's block table.  It serves a portion of a prompt
 // and a single decoded token alike (every row carries its own position), any head size
 // up to 256, any group size, float32 or bfloat16 storage; all arithmetic is float32.
+// Values may have another size than keys (vd), a score may be capped,
+// s <- cap * tanh(s / cap), and a head's output may be multiplied by the sigmoid of a gate
+// value of its own (one float32 per row and head).
 //
 // For head h, kv head = h / (heads / kv_heads); keys t in [from, p] with
 // from = p + 1 - w when w > 0 and p + 1 > w, else 0; s_t = (q . k_t) * scale; softmax
@@ -24,13 +27,14 @@ template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
     const TQ* __restrict__ q, TO* __restrict__ out, const TC* __restrict__ kplane, const TC* __restrict__ vplane,
     const int* __restrict__ positions, const int* __restrict__ row_req, const int* __restrict__ table,
-    int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int window, float scale) {
+    int table_stride, int page_tokens, int n_heads, int n_kv, int hd, int vd, int window, float scale, float softcap,
+    const float* __restrict__ head_gate, int gate_ld) {
     cj::after_predecessor();
     cj::release_successor();
     extern __shared__ float smem[];
     float* qs = smem;                       // [hd]
-    float* acc_s = smem + hd;               // [WARPS][hd]
-    float* m_s = acc_s + WARPS * hd;        // [WARPS]
+    float* acc_s = smem + hd;               // [WARPS][vd]
+    float* m_s = acc_s + WARPS * vd;        // [WARPS]
     float* l_s = m_s + WARPS;               // [WARPS]
 
     int h = blockIdx.y, t = blockIdx.x;
@@ -55,14 +59,15 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
         int key = from + c * 32 + lane;
         bool valid = key <= p;
         float s = -INFINITY;
-        size_t base = 0;
+        size_t base = 0;                    // the key's place in units of one (token, head) entry
         if (valid) {
             int page = tab[key / page_tokens];
-            base = (((size_t)page * n_kv + kvh) * page_tokens + key % page_tokens) * hd;
-            const TC* kr = kplane + base;
+            base = ((size_t)page * n_kv + kvh) * page_tokens + key % page_tokens;
+            const TC* kr = kplane + base * hd;
             float dot = 0.0f;
             for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f32(kr[d]), dot);
             s = dot * scale;
+            if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
         }
         float cmax = warp_max(s);
         float m_new = fmaxf(m, cmax);
@@ -75,11 +80,11 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
         for (int j = 0; j < in_chunk; ++j) {
             float ej = __shfl_sync(0xffffffffu, e, j);
             size_t bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
-            const TC* vr = vplane + bj;
+            const TC* vr = vplane + bj * vd;
 #pragma unroll
             for (int i = 0; i < DPL; ++i) {
                 int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(ej, to_f32(vr[d]), acc[i]);
+                if (d < vd) acc[i] = fmaf(ej, to_f32(vr[d]), acc[i]);
             }
         }
         m = m_new;
@@ -89,7 +94,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
         int d = lane + 32 * i;
-        if (d < hd) acc_s[warp * hd + d] = acc[i];
+        if (d < vd) acc_s[warp * vd + d] = acc[i];
     }
     __syncthreads();
     float mx = m_s[0];
@@ -103,33 +108,125 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(
         lsum += l_s[w] * f[w];
     }
     float inv = 1.0f / lsum;
-    TO* orow = out + ((size_t)t * n_heads + h) * hd;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    if (head_gate) inv *= 1.0f / (1.0f + expf(-head_gate[(size_t)t * gate_ld + h]));
+    TO* orow = out + ((size_t)t * n_heads + h) * vd;
+    for (int d = threadIdx.x; d < vd; d += blockDim.x) {
         float o = 0.0f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) o += acc_s[w * hd + d] * f[w];
+        for (int w = 0; w < WARPS; ++w) o += acc_s[w * vd + d] * f[w];
         orow[d] = from_f32<TO>(o * inv);
     }
 }
 
 }  // namespace
 
-// q, out: [T, n_heads, hd] in the activation dtype; planes: [pages, n_kv, page_tokens, hd].
+// q [T, n_heads, hd], out [T, n_heads, vd] in the activation dtype; planes [pages, n_kv, page_tokens, hd | vd].
+// softcap 0: none.  head_gate: null, or float32 with row stride gate_ld whose entry [t, h] gates head h of row t.
 CJ_EXPORT int cj_paged_attention(const void* q, void* out, int act_dtype, const void* kplane, const void* vplane,
                                  int cache_dtype, const int* positions, const int* row_req, const int* table,
-                                 int table_stride, int page_tokens, int T, int n_heads, int n_kv, int hd,
-                                 int window, float scale, cudaStream_t stream) {
+                                 int table_stride, int page_tokens, int T, int n_heads, int n_kv, int hd, int vd,
+                                 int window, float scale, float softcap, const float* head_gate, int gate_ld,
+                                 cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !positions || !row_req || !table) return CJ_ERR_ARG;
+    if (vd <= 0 || vd > MAX_HD) return CJ_ERR_SIZE;
     if (hd <= 0 || hd > MAX_HD || n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
     if (n_heads > 65535) return CJ_ERR_SIZE;
     dim3 grid(T, n_heads);
-    size_t smem = (size_t)(hd + WARPS * hd + 2 * WARPS) * sizeof(float);
+    size_t smem = (size_t)(hd + WARPS * vd + 2 * WARPS) * sizeof(float);
 #define LAUNCH(TQ, TC)                                                                                             \
     cj::launch(paged_attention_kernel<TQ, TC, TQ>, dim3(grid), dim3(WARPS * 32), smem, stream, (const TQ*)q, (TQ*)out, (const TC*)kplane, \
-        (const TC*)vplane, positions, row_req, table, table_stride, page_tokens, n_heads, n_kv, hd, window, scale)
+        (const TC*)vplane, positions, row_req, table, table_stride, page_tokens, n_heads, n_kv, hd, vd, window, scale, softcap, \
+        head_gate, gate_ld)
     if (act_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
     else if (act_dtype == CJ_BF16 && cache_dtype == CJ_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return CJ_ERR_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------
+// Heads of a step's rows made ready for attention, one warp per (row, head): the
+// queries' and keys' heads are RMS-normed over the head (x / sqrt(mean x^2 + eps) * w[d],
+// one weight vector shared by the heads) when a weight is given; their first `rot` entries
+// are rotated at the row's position, entry i paired with entry i + rot/2:
+//   (a, b) -> (a cos - b sin, b cos + a sin), angle = float(p) * inv_freq[i],
+// cos and sin multiplied by `magnitude`; queries go to q_out, keys and values to the row's
+// place in the paged cache.  v_off < 0: the values are the keys as projected, before norm
+// and rotation (vd == hd then).  All arithmetic is float32.
+// ---------------------------------------------------------------------------------
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(128) head_prepare_kernel(
+    const float* __restrict__ x, int ld, int q_off, int k_off, int v_off, TQ* __restrict__ q_out, TC* __restrict__ kplane,
+    TC* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req, const int* __restrict__ table,
+    int table_stride, int page_tokens, int T, int n_heads, int n_kv, int hd, int vd, int rot, const float* __restrict__ inv_freq,
+    float magnitude, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int write_kv) {
+    cj::after_predecessor();
+    cj::release_successor();
+    const int lane = threadIdx.x & 31;
+    const int slots = n_heads + (write_kv ? n_kv : 0);
+    const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (unit >= (long long)T * slots) return;
+    const int t = (int)(unit / slots), slot = (int)(unit % slots);
+    const bool is_q = slot < n_heads;
+    const int head = is_q ? slot : slot - n_heads;
+    const float* src = x + (size_t)t * ld + (is_q ? q_off : k_off) + head * hd;
+    const float* nw = is_q ? q_norm : k_norm;
+    const int pos = positions[t];
+    float inv = 1.0f;
+    if (nw) {
+        float ss = 0.0f;
+        for (int d = lane; d < hd; d += 32) ss = fmaf(src[d], src[d], ss);
+        ss = warp_sum(ss);
+        inv = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    size_t place = 0;
+    bool have_page = false;
+    if (!is_q) {
+        int page = table[(size_t)row_req[t] * table_stride + pos / page_tokens];
+        have_page = page >= 0;                       // no page: the host never schedules this
+        place = ((size_t)(have_page ? page : 0) * n_kv + head) * page_tokens + pos % page_tokens;
+        if (!have_page) return;
+    }
+    const int half = rot >> 1;
+    for (int d = lane; d < hd; d += 32) {
+        float a = src[d] * inv * (nw ? nw[d] : 1.0f);
+        float r = a;
+        if (d < rot) {
+            const int i = d < half ? d : d - half, pd = d < half ? d + half : d - half;
+            const float b = src[pd] * inv * (nw ? nw[pd] : 1.0f);
+            const float ang = (float)pos * inv_freq[i];
+            const float c = cosf(ang) * magnitude, s = sinf(ang) * magnitude;
+            r = d < half ? a * c - b * s : a * c + b * s;
+        }
+        if (is_q) q_out[((size_t)t * n_heads + head) * hd + d] = from_f32<TQ>(r);
+        else kplane[place * hd + d] = from_f32<TC>(r);
+    }
+    if (!is_q) {
+        const float* vs = v_off < 0 ? src : x + (size_t)t * ld + v_off + head * vd;
+        for (int d = lane; d < vd; d += 32) vplane[place * vd + d] = from_f32<TC>(vs[d]);
+    }
+}
+
+CJ_EXPORT int cj_head_prepare(const float* x, int ld, int q_off, int k_off, int v_off, void* q_out, int q_dtype, void* kplane,
+                              void* vplane, int cache_dtype, const int* positions, const int* row_req, const int* table,
+                              int table_stride, int page_tokens, int T, int n_heads, int n_kv, int hd, int vd, int rotary_dim,
+                              const float* inv_freq, float magnitude, const float* q_norm, const float* k_norm, float eps,
+                              int write_kv, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (!x || !q_out || !positions || n_heads <= 0 || hd <= 0 || vd <= 0) return CJ_ERR_ARG;
+    if (rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1)) return CJ_ERR_SIZE;
+    if (rotary_dim > 0 && !inv_freq) return CJ_ERR_ARG;
+    if (write_kv && (!kplane || !vplane || !row_req || !table || page_tokens <= 0 || n_kv <= 0)) return CJ_ERR_ARG;
+    if (v_off < 0 && vd != hd) return CJ_ERR_SIZE;
+    const long long units = (long long)T * (n_heads + (write_kv ? n_kv : 0));
+    dim3 grid((unsigned)((units + 3) / 4));
+#define LAUNCH(TQ, TC)                                                                                                  \
+    cj::launch(head_prepare_kernel<TQ, TC>, dim3(grid), dim3(128), 0, stream, x, ld, q_off, k_off, v_off, (TQ*)q_out,  \
+        (TC*)kplane, (TC*)vplane, positions, row_req, table, table_stride, page_tokens, T, n_heads, n_kv, hd, vd,      \
+        rotary_dim, inv_freq, magnitude, q_norm, k_norm, eps, write_kv)
+    if (q_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);
+    else if (q_dtype == CJ_BF16 && cache_dtype == CJ_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else return CJ_ERR_DTYPE;
 #undef LAUNCH
     return launch_status();

@@ -45,6 +45,7 @@ LIBRARIES: Dict[str, str] = {
     "recurrent": "recurrent.cu",
     "latent_attention": "latent_attention.cu",
     "latent_prefill": "latent_prefill.cu",
+    "stream_ops": "stream_ops.cu",
 }
 HEADERS = ["common.cuh", "tc_common.cuh", "sampling_static.h"]
 

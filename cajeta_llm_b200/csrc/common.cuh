@@ -46,6 +46,27 @@ __device__ __forceinline__ float warp_max(float v) {
 // x / (1 + exp(-x)), the reference's SiLU (model/Prim.cajeta:1822-1847)
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
+// The gate of a gated feed-forward, from its two products g (gate) and u (up).  limit == 0:
+// silu(g) * u.  limit > 0, the capped form: g = min(g, limit), u = clamp(u, -limit, limit),
+// g * sigmoid(alpha g) * (u + 1).
+__device__ __forceinline__ float gated_act(float g, float u, float limit, float alpha) {
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    }
+    return silu(g) * u;
+}
+// the same with the fast exponential and division, for results that are rounded to bfloat16
+__device__ __forceinline__ float gated_act_fast(float g, float u, float limit, float alpha) {
+    if (limit > 0.0f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+    }
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 // Launches overlap their neighbours in the stream (programmatic dependent launch): a kernel
 // may be set up on the SMs while the one before it is still draining.  Every kernel of this
 // library therefore begins with after_predecessor(), which returns once all earlier work in

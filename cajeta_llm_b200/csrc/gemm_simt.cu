@@ -32,6 +32,7 @@ struct GemmArgs {
     const int* a_row_index;       // [M] or null
     long long w_group_stride;
     int num_groups;
+    float act_limit, act_alpha;   // the gated form's activation (see gated_act)
 };
 
 template <typename TA, typename TW, typename TC, bool SWIGLU>
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs p) {
             int c = col_begin + tx * TN + j;
             if (c >= p.N) continue;
             float v = acc[i][j];
-            if (SWIGLU) v = silu(v) * acc2[i][j];
+            if (SWIGLU) v = gated_act(v, acc2[i][j], p.act_limit, p.act_alpha);
             if (p.bias) v += p.bias[c];
             size_t o = (size_t)r * p.ldc + c;
             if (p.accumulate) v += to_f32(C[o]);
@@ -166,11 +167,11 @@ int launch(const GemmArgs& p, bool swiglu, cudaStream_t stream) {
 CJ_EXPORT int cj_gemm_simt(const void* A, long long lda, int a_dtype, const void* W, const void* W2, long long ldw,
                            int w_dtype, const float* bias, void* C, long long ldc, int c_dtype, int M, int N, int K,
                            int accumulate, const int* group_offsets, int num_groups, long long w_group_stride,
-                           const int* a_row_index, cudaStream_t stream) {
+                           const int* a_row_index, float act_limit, float act_alpha, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!A || !W || !C || K <= 0) return CJ_ERR_ARG;
     if (group_offsets && num_groups <= 0) return CJ_ERR_ARG;
-    GemmArgs p{A, lda, W, W2, ldw, bias, C, ldc, M, N, K, accumulate, group_offsets, a_row_index, w_group_stride, num_groups};
+    GemmArgs p{A, lda, W, W2, ldw, bias, C, ldc, M, N, K, accumulate, group_offsets, a_row_index, w_group_stride, num_groups, act_limit, act_alpha};
     bool sw = W2 != nullptr;
     if (a_dtype == CJ_F32 && w_dtype == CJ_F32 && c_dtype == CJ_F32) return launch<float, float, float>(p, sw, stream);
     if (a_dtype == CJ_BF16 && w_dtype == CJ_BF16 && c_dtype == CJ_F32) return launch<__nv_bfloat16, __nv_bfloat16, float>(p, sw, stream);

@@ -54,6 +54,7 @@ struct Args {
     int k_splits;               // > 1: each split stores its partial at out + split * split_stride
     long long split_stride;
     int offsets_settled;        // the groups' offsets were complete before the kernel before this one began
+    float act_limit, act_alpha; // the gated form's activation (see gated_act)
     int choose_height;          // grouped, weights on the rows: the tile's height is chosen in the kernel (see LowTiles)
 };
 
@@ -366,7 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int j = 0; j < 16; ++j) {
                     v[j] = __uint_as_float(v0[j]);
                     // the result is rounded to bfloat16 (8 bits): the fast exponential and division (2 ulp of float32) do not show
-                    if (EPI == EPI_SWIGLU_BF16) v[j] = __fdividef(v[j], 1.0f + __expf(-v[j])) * __uint_as_float(v1[j]);
+                    if (EPI == EPI_SWIGLU_BF16) v[j] = cj::gated_act_fast(v[j], __uint_as_float(v1[j]), p.act_limit, p.act_alpha);
                 }
                 if (!SWAP) {
                     // this thread owns one token row and 16 consecutive features of it
@@ -537,7 +538,7 @@ int dispatch_n(int n_mma, const CUtensorMap& mx, const CUtensorMap& mw, const CU
 CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void* w2, const float* bias, void* out,
                          long long ldo, int tokens, int features, int K, int epilogue, int swap, int n_mma,
                          const int* group_offsets, int groups, int k_splits, long long split_stride,
-                         int offsets_settled, cudaStream_t stream) {
+                         int offsets_settled, float act_limit, float act_alpha, cudaStream_t stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (!x || !w || !out || K <= 0) return CJ_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0) return CJ_ERR_ALIGN;               // TMA: 16-byte strides
@@ -563,7 +564,7 @@ CJ_EXPORT int cj_gemm_tc(const void* x, long long ldx, const void* w, const void
             if (w2 && !make_map_bf16(&low.w2[i], w2, total_w_rows, K, K, low_height(i))) return CJ_ERR_ARG;
         }
     }
-    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, k_splits, split_stride, offsets_settled, choose_height};
+    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, k_splits, split_stride, offsets_settled, act_limit, act_alpha, choose_height};
 #define CASE(EPI, DUAL)                                                                              \
     if (swap) return dispatch_n<true, DUAL, EPI>(n_mma, mx, mw, mw2, low, a, stream);                 \
     else return dispatch_n<false, DUAL, EPI>(n_mma, mx, mw, mw2, low, a, stream);

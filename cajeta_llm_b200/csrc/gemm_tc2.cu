@@ -55,6 +55,7 @@ struct Args {
     const float* bias;
     const int* group_offsets;
     int groups;
+    float act_limit, act_alpha;  // the gated form's activation (see gated_act)
 };
 
 template <int N_TOK, int STAGES>
@@ -444,7 +445,7 @@ swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         float gv = __uint_as_float(g[j]);
-                        v[j] = gv * __frcp_rn(1.0f + __expf(-gv)) * __uint_as_float(u[j]);
+                        v[j] = cj::gated_act_fast(gv, __uint_as_float(u[j]), p.act_limit, p.act_alpha);
                     }
                     __nv_bfloat16* dst = dst_row + c0;
                     if (c.feat0 + c0 + 16 <= p.features && (((uintptr_t)dst) & 15) == 0) {
@@ -553,7 +554,7 @@ int launch_swiglu(const CUtensorMap& mx, const CUtensorMap& mwg, const CUtensorM
 // Refuses (negative code) what it cannot run; never a wrong result.
 CJ_EXPORT int cj_gemm_tc2(const void* x, long long ldx, const void* w, const void* w2, const float* bias, void* out,
                           long long ldo, int tokens, int features, int K, int epilogue, int n_tok,
-                          const int* group_offsets, int groups, cudaStream_t stream) {
+                          const int* group_offsets, int groups, float act_limit, float act_alpha, cudaStream_t stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (!x || !w || !out || K <= 0) return CJ_ERR_ARG;
     if (K % 8 != 0 || ldx % 8 != 0) return CJ_ERR_ALIGN;
@@ -566,7 +567,7 @@ CJ_EXPORT int cj_gemm_tc2(const void* x, long long ldx, const void* w, const voi
     int total_w_rows = (group_offsets ? groups : 1) * features;
     CUtensorMap mx, mw, mw2;
     if (!make_map_bf16(&mw, w, total_w_rows, K, K, 128)) return CJ_ERR_ARG;
-    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups};
+    Args a{tokens, features, K, out, ldo, bias, group_offsets, groups, act_limit, act_alpha};
     if (epilogue == EPI_SWIGLU_BF16) {
         // tokens on the rows: a block's box is 128 token rows whatever n_tok says
         if (!make_map_bf16(&mx, x, tokens, K, ldx, 128)) return CJ_ERR_ARG;

@@ -162,10 +162,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
          accumulate: bool = False, w_up: Optional[torch.Tensor] = None, group_offsets: Optional[torch.Tensor] = None,
-         a_row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
+         a_row_index: Optional[torch.Tensor] = None, rows: Optional[int] = None, act_limit: float = 0.0,
+         act_alpha: float = 1.0) -> None:
     """out[M, N] (+)= a[M, K] . w[N, K]^T (+ bias) on the float32 FMA pipe.
 
-    ``w_up`` selects the SwiGLU form silu(a.w^T) * (a.w_up^T).  With ``group_offsets``
+    ``w_up`` selects the gated form: silu(a.w^T) * (a.w_up^T), or with ``act_limit`` > 0 the capped one,
+    g = min(a.w^T, limit), u = clamp(a.w_up^T, +-limit), g * sigmoid(act_alpha g) * (u + 1).  With ``group_offsets``
     ([G + 1] int32) ``w`` is [G, N, K], output row s belongs to the group whose range
     holds s, and ``a_row_index[s]`` names the row of ``a`` that feeds it.
     """
@@ -192,7 +194,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[tor
     st = library("gemm_simt").cj_gemm_simt(
         _ptr(a), _ll(a.stride(0)), _i(_code(a)), _ptr(w), _ptr(w_up), _ll(K), _i(_code(w)), _ptr(bias),
         _ptr(out), _ll(out.stride(0)), _i(_code(out)), _i(M), _i(N), _i(K), _i(1 if accumulate else 0),
-        _ptr(group_offsets), _i(G), _ll(N * K), _ptr(a_row_index), _stream())
+        _ptr(group_offsets), _i(G), _ll(N * K), _ptr(a_row_index), _f(act_limit), _f(act_alpha), _stream())
     _check(st, "gemm")
 
 
@@ -216,20 +218,67 @@ def rope_kv_write(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: 
     _check(st, "rope_kv_write")
 
 
+def head_prepare(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, k_plane: Optional[torch.Tensor],
+                 v_plane: Optional[torch.Tensor], positions: torch.Tensor, row_req: Optional[torch.Tensor],
+                 table: Optional[torch.Tensor], page_tokens: int, n_heads: int, n_kv: int, head_dim: int, value_dim: int,
+                 rotary_dim: int, inv_freq: Optional[torch.Tensor], magnitude: float, q_norm: Optional[torch.Tensor],
+                 k_norm: Optional[torch.Tensor], eps: float, write_kv: bool) -> None:
+    """Queries, keys and values of a step's rows (x float32 [T, ld], columns from q_off, k_off, v_off) made ready
+    for attention: an RMS norm over each head of q and k (when ``q_norm`` / ``k_norm``, float32 [head_dim], are
+    given), the rotation of their first ``rotary_dim`` entries (entry i with i + rotary_dim / 2; cos and sin times
+    ``magnitude``), q to ``q_out``, k and v into the cache pages of the row's request.  ``v_off`` < 0: the
+    values are the keys as projected, before norm and rotation."""
+    _need(x, "x", torch.float32), _need(q_out, "q_out"), _need(positions, "positions", torch.int32)
+    cache_dtype = _code(q_out)
+    if write_kv:
+        _need(k_plane, "k_plane"), _need(v_plane, "v_plane"), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
+        cache_dtype = _code(k_plane)
+        if k_plane.shape[-1] != head_dim or v_plane.shape[-1] != value_dim:
+            raise KernelError("head_prepare: the cache planes do not have the heads' sizes")
+    for n, t in (("q_norm", q_norm), ("k_norm", k_norm), ("inv_freq", inv_freq)):
+        if t is not None:
+            _need(t, n, torch.float32)
+    st = library("attention_paged").cj_head_prepare(
+        _ptr(x), _i(x.stride(0)), _i(q_off), _i(k_off), _i(v_off), _ptr(q_out), _i(_code(q_out)), _ptr(k_plane), _ptr(v_plane),
+        _i(cache_dtype), _ptr(positions), _ptr(row_req), _ptr(table), _i(table.stride(0) if table is not None else 0),
+        _i(page_tokens), _i(x.shape[0]), _i(n_heads), _i(n_kv), _i(head_dim), _i(value_dim), _i(rotary_dim), _ptr(inv_freq),
+        _f(magnitude), _ptr(q_norm), _ptr(k_norm), _f(eps), _i(1 if write_kv else 0), _stream())
+    _check(st, "head_prepare")
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                     positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
-                    n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
-    """Attention of every row over its request's cached keys [from, position]."""
+                    n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, value_dim: int = 0,
+                    softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
+    """Attention of every row over its request's cached keys [from, position].  ``value_dim``: the values'
+    size when it is not the keys'; ``softcap`` > 0: s <- cap tanh(s / cap); ``head_gate`` (float32 [T, ld]):
+    head h of row t is multiplied by sigmoid(head_gate[t, gate_offset + h])."""
     _need(q, "q"), _need(out, "out"), _need(k_plane, "k_plane"), _need(v_plane, "v_plane")
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     T = q.shape[0]
     if head_dim > 256:
         raise KernelError(f"paged_attention: head_dim {head_dim} is larger than 256")
+    gate_ptr, gate_ld = ctypes.c_void_p(0), 0
+    if head_gate is not None:
+        _need(head_gate, "head_gate", torch.float32)
+        gate_ptr, gate_ld = ctypes.c_void_p(head_gate.data_ptr() + 4 * gate_offset), head_gate.stride(0)
     st = library("attention_paged").cj_paged_attention(
         _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_plane), _ptr(v_plane), _i(_code(k_plane)), _ptr(positions),
         _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim),
-        _i(window), _f(scale), _stream())
+        _i(value_dim or head_dim), _i(window), _f(scale), _f(softcap), gate_ptr, _i(gate_ld), _stream())
     _check(st, "paged_attention")
+
+
+def _route_mode(norm_topk: bool, sigmoid_scores: bool, groups) -> int:
+    """The selection's mode word: bit 0 renormalise the picked scores, bit 1 sigmoid scores, bits 4-15 the
+    number of expert groups and bits 16-27 how many of them stay eligible (``groups`` = (count, keep))."""
+    mode = (1 if norm_topk else 0) | (2 if sigmoid_scores else 0)
+    if groups is not None and int(groups[0]) > 1:
+        count, keep = int(groups[0]), int(groups[1])
+        if not (1 <= keep <= count <= 0xfff):
+            raise KernelError(f"router: {keep} of {count} expert groups cannot be kept")
+        mode |= (count << 4) | (keep << 16)
+    return mode
 
 
 def _pin_and_gap(pin: Optional[torch.Tensor], gap: Optional[torch.Tensor], T: int, top_k: int) -> None:
@@ -245,12 +294,14 @@ def _pin_and_gap(pin: Optional[torch.Tensor], gap: Optional[torch.Tensor], T: in
 
 def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[torch.Tensor], top_k: int,
                 norm_topk: bool, sel: torch.Tensor, weights: torch.Tensor, shared_scale: Optional[torch.Tensor],
-                pin: Optional[torch.Tensor] = None, gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False) -> None:
+                pin: Optional[torch.Tensor] = None, gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False,
+                groups=None) -> None:
     """Router logits, softmax over all experts (or, with ``sigmoid_scores``, each expert's own
     sigmoid), top-k and the shared expert's sigmoid gate.
     ``pin`` (int32 [T, k]): the experts are given, not chosen; the weights are still the row's own
     probabilities of them.  ``gap`` (float32 [T], not with ``pin``): each row's routing margin
-    (p_k - p_{k+1}) / p_k out."""
+    (p_k - p_{k+1}) / p_k out.  ``groups`` = (count, keep): the experts form ``count`` equal groups of
+    neighbours and only those of the ``keep`` groups with the largest best score can be picked."""
     _need(x, "x", torch.float32), _need(router_w, "router_w", torch.float32)
     _need(sel, "sel", torch.int32), _need(weights, "weights", torch.float32)
     T, H = x.shape
@@ -258,6 +309,8 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
     _pin_and_gap(pin, gap, T, top_k)
     if E > 1024:
         raise KernelError(f"router_topk: {E} experts; this kernel takes at most 1024")
+    if groups is not None and int(groups[0]) > 1 and E % int(groups[0]) != 0:
+        raise KernelError(f"router_topk: {E} experts do not form {groups[0]} equal groups")
     if shared_gate is not None:
         _need(shared_gate, "shared_gate", torch.float32), _need(shared_scale, "shared_scale", torch.float32)
     logits = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)
@@ -265,7 +318,7 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
     if tickets is None:
         tickets = _router_tickets[x.device] = torch.zeros((4,), dtype=torch.int32, device=x.device)
     st = library("moe_route").cj_router_topk(_ptr(x), _ptr(router_w), _ptr(shared_gate), _i(T), _i(H), _i(E), _i(top_k),
-                                             _i((1 if norm_topk else 0) | (2 if sigmoid_scores else 0)), _ptr(sel), _ptr(weights),
+                                             _i(_route_mode(norm_topk, sigmoid_scores, groups)), _ptr(sel), _ptr(weights),
                                              _ptr(shared_scale), _ptr(logits), _ptr(tickets), _ptr(pin), _ptr(gap), _stream())
     _check(st, "router_topk")
     if T > 32:
@@ -275,7 +328,7 @@ def router_topk(x: torch.Tensor, router_w: torch.Tensor, shared_gate: Optional[t
 
 def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_topk: bool, sel: torch.Tensor,
                   weights: torch.Tensor, shared_scale: Optional[torch.Tensor], pin: Optional[torch.Tensor] = None,
-                  gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False) -> None:
+                  gap: Optional[torch.Tensor] = None, sigmoid_scores: bool = False, groups=None) -> None:
     """Softmax over all experts, top-k and the shared gate's sigmoid from router logits given
     as partial sums ``[S, T, ld]`` (float32; column ``num_experts`` holds the gate's dot when
     ``shared_scale`` is given); the partials of a row are added in order first."""
@@ -289,7 +342,7 @@ def router_select(partials: torch.Tensor, num_experts: int, top_k: int, norm_top
     if shared_scale is not None:
         _need(shared_scale, "shared_scale", torch.float32)
     st = library("moe_route").cj_router_select(_ptr(partials), _i(S), _ll(partials.stride(0)), _i(ld), _i(T), _i(num_experts),
-                                               _i(top_k), _i((1 if norm_topk else 0) | (2 if sigmoid_scores else 0)), _ptr(sel),
+                                               _i(top_k), _i(_route_mode(norm_topk, sigmoid_scores, groups)), _ptr(sel),
                                                _ptr(weights), _ptr(shared_scale), _ptr(pin), _ptr(gap), _stream())
     _check(st, "router_select")
 
@@ -326,6 +379,76 @@ def moe_combine(hs: torch.Tensor, y: Optional[torch.Tensor], slot_of_pick: Optio
     st = library("rowwise").cj_moe_combine(_ptr(hs), _ptr(y), _ptr(slot_of_pick), _ptr(weights), _i(top_k), _ptr(shared),
                                            _i(chunks), _ll(stride), _ptr(shared_scale), _i(T), _i(H), _stream())
     _check(st, "moe_combine")
+
+
+# -- steps on the residual stream between layers ---------------------------------------------------------
+def pair_embed(out: torch.Tensor, table: torch.Tensor, pair: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+               row_req: torch.Tensor, req_start: torch.Tensor, req_slot: torch.Tensor, state: torch.Tensor, buckets: int,
+               mul_prev: int, mul_cur: int) -> None:
+    """out[t] = table[ids[t]] + pair[(prev * mul_prev + ids[t] * mul_cur) mod buckets], or pair[buckets] at position 0;
+    prev is the row before within the request, or ``state[slot]`` (int32, the request's last token of the step
+    before) for its first row of the step.  out float32 [T, H]."""
+    _need(out, "out", torch.float32), _need(table, "table"), _need(pair, "pair", table.dtype), _need(state, "state", torch.int32)
+    for n, t in (("ids", ids), ("positions", positions), ("row_req", row_req), ("req_start", req_start), ("req_slot", req_slot)):
+        _need(t, n, torch.int32)
+    T, H = out.shape
+    if pair.shape != (buckets + 1, H) or table.shape[1] != H:
+        raise KernelError(f"pair_embed: tables {tuple(table.shape)} and {tuple(pair.shape)} do not fit {buckets} buckets of {H}")
+    st = library("stream_ops").cj_pair_embed(_ptr(out), _ptr(table), _ptr(pair), _i(_code(table)), _ptr(ids), _ptr(positions),
+                                             _ptr(row_req), _ptr(req_start), _ptr(req_slot), _ptr(state), _i(T), _i(H),
+                                             _i(table.shape[0]), _i(buckets), _ll(mul_prev), _ll(mul_cur), _stream())
+    _check(st, "pair_embed")
+
+
+def pair_commit(ids: torch.Tensor, req_start: torch.Tensor, req_slot: torch.Tensor, state: torch.Tensor, requests: int) -> None:
+    """After ``pair_embed``: every request's last token of the step becomes its ``state`` entry."""
+    _need(ids, "ids", torch.int32), _need(req_start, "req_start", torch.int32), _need(req_slot, "req_slot", torch.int32)
+    _need(state, "state", torch.int32)
+    _check(library("stream_ops").cj_pair_commit(_ptr(ids), _ptr(req_start), _ptr(req_slot), _ptr(state), _i(requests), _stream()),
+           "pair_commit")
+
+
+def add_rows(hs: torch.Tensor, other: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> None:
+    """hs[t] += other[t] + vec; everything float32; either may be None."""
+    _need(hs, "hs", torch.float32)
+    T, H = hs.shape
+    if other is not None:
+        _need(other, "other", torch.float32)
+        if other.shape != hs.shape:
+            raise KernelError("add_rows: shapes differ")
+    if vec is not None:
+        _need(vec, "vec", torch.float32)
+        if vec.numel() != H:
+            raise KernelError("add_rows: the vector does not have the rows' width")
+    _check(library("stream_ops").cj_add_rows(_ptr(hs), _ptr(other), _ptr(vec), _i(T), _i(H), _stream()), "add_rows")
+
+
+def gelu_gate(a: torch.Tensor, table: torch.Tensor, offset: int, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(a[t, j]) * table[ids[t], offset + j]; a float32 [T, >= n], out [T, n] in the table's dtype."""
+    _need(a, "a", torch.float32), _need(table, "table"), _need(ids, "ids", torch.int32), _need(out, "out", table.dtype)
+    T, n = out.shape
+    if a.shape[1] < n or table.shape[1] < offset + n:
+        raise KernelError("gelu_gate: sizes do not agree")
+    st = library("stream_ops").cj_gelu_gate(_ptr(a), _i(a.stride(0)), _ptr(table), _i(_code(table)), _i(table.stride(0)), _i(offset),
+                                            _ptr(ids), _i(table.shape[0]), _ptr(out), _i(_code(out)), _i(T), _i(n), _stream())
+    _check(st, "gelu_gate")
+
+
+def stream_cast(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32) in out's dtype."""
+    _need(x, "x", torch.float32), _need(out, "out")
+    if out.numel() != x.numel():
+        raise KernelError("stream_cast: sizes differ")
+    _check(library("stream_ops").cj_stream_cast(_ptr(x), _ptr(out), _i(_code(out)), _ll(x.numel()), _stream()), "stream_cast")
+
+
+def stream_norm_add(hs: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """hs[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight; everything float32."""
+    _need(hs, "hs", torch.float32), _need(y, "y", torch.float32), _need(weight, "weight", torch.float32)
+    T, H = hs.shape
+    if y.shape != hs.shape or weight.numel() != H:
+        raise KernelError("stream_norm_add: shapes do not agree")
+    _check(library("stream_ops").cj_stream_norm_add(_ptr(hs), _ptr(y), _ptr(weight), _f(eps), _i(T), _i(H), _stream()), "stream_norm_add")
 
 
 # -- a block that norms a sublayer's output; mixers with a state per request -----------------------------
@@ -636,7 +759,7 @@ EPI_STORE_F32, EPI_ACC_F32, EPI_SWIGLU_BF16, EPI_STORE_BF16 = 0, 1, 2, 3
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, swap: bool, n_mma: int,
             bias: Optional[torch.Tensor] = None, w_up: Optional[torch.Tensor] = None,
             group_offsets: Optional[torch.Tensor] = None, tokens: Optional[int] = None, k_splits: int = 1,
-            offsets_settled: bool = False) -> None:
+            offsets_settled: bool = False, act_limit: float = 0.0, act_alpha: float = 1.0) -> None:
     """Tensor-core product out[token, feature] (+)= x[token, :] . w[feature, :] (+ bias) in
     bfloat16 with float32 accumulation (tcgen05, TMA).
 
@@ -669,13 +792,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     st = library("gemm_tc").cj_gemm_tc(
         _ptr(x), _ll(x.stride(0)), _ptr(w), _ptr(w_up), _ptr(bias), _ptr(out), _ll(ldo), _i(T), _i(features), _i(K),
         _i(epilogue), _i(1 if swap else 0), _i(n_mma), _ptr(group_offsets), _i(G), _i(k_splits), _ll(split_stride),
-        _i(1 if offsets_settled and group_offsets is not None else 0), _stream())
+        _i(1 if offsets_settled and group_offsets is not None else 0), _f(act_limit), _f(act_alpha), _stream())
     _check(st, "gemm_tc")
 
 
 def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, n_tok: int,
              bias: Optional[torch.Tensor] = None, w_up: Optional[torch.Tensor] = None,
-             group_offsets: Optional[torch.Tensor] = None, tokens: Optional[int] = None) -> None:
+             group_offsets: Optional[torch.Tensor] = None, tokens: Optional[int] = None, act_limit: float = 0.0,
+             act_alpha: float = 1.0) -> None:
     """The same product as ``gemm_tc`` on pairs of SMs (tcgen05 cta_group::2): tiles of 256
     features x ``n_tok`` (128 or 256) tokens, each SM of a pair loading its own 128 weight rows
     and half of the token rows.  For steps with many rows."""
@@ -697,7 +821,7 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int,
         G = w.shape[0]
     st = library("gemm_tc2").cj_gemm_tc2(
         _ptr(x), _ll(x.stride(0)), _ptr(w), _ptr(w_up), _ptr(bias), _ptr(out), _ll(out.stride(-2)), _i(T), _i(features), _i(K),
-        _i(epilogue), _i(n_tok), _ptr(group_offsets), _i(G), _stream())
+        _i(epilogue), _i(n_tok), _ptr(group_offsets), _i(G), _f(act_limit), _f(act_alpha), _stream())
     _check(st, "gemm_tc2")
 
 

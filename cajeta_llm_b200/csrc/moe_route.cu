@@ -111,6 +111,9 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
     // bit 1 of norm_topk: an expert's score is the sigmoid of its own logit instead of the
     // softmax over all experts (bit 0 still asks for the picked scores to be renormalised)
     const bool sigmoid_scores = (norm_topk & 2) != 0;
+    // bits 4-15: the experts form that many equal groups of neighbours (0 or 1: no groups), bits 16-27:
+    // only the experts of that many groups - those whose best score is largest - can be picked
+    const int n_groups = (norm_topk >> 4) & 0xfff, keep_groups = (norm_topk >> 16) & 0xfff;
     norm_topk &= 1;
     if (sigmoid_scores) {
         for (int e = lane; e < E; e += 32) probs[e] = 1.0f / (1.0f + expf(-row[e]));
@@ -145,6 +148,30 @@ __device__ __forceinline__ void select_row(const float* row, int t, int E, int k
             }
         }
         return;
+    }
+    if (n_groups > 1 && keep_groups < n_groups) {
+        // the groups with the smallest best score leave one by one (of equal ones the later group
+        // first): their experts' scores become -1, which no pick takes
+        const int per = E / n_groups;
+        for (int drop = n_groups - keep_groups; drop > 0; --drop) {
+            float wm = 0.0f;
+            int worst = -1;
+            for (int g = lane; g < n_groups; g += 32) {
+                float m = -1.0f;
+                for (int i = 0; i < per; ++i) m = fmaxf(m, probs[g * per + i]);
+                if (m >= 0.0f && (worst < 0 || m <= wm)) { worst = g; wm = m; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                float om = __shfl_xor_sync(0xffffffffu, wm, o);
+                int ow = __shfl_xor_sync(0xffffffffu, worst, o);
+                bool take = ow >= 0 && (worst < 0 || om < wm || (om == wm && ow > worst));
+                if (take) { wm = om; worst = ow; }
+            }
+            if (worst < 0) break;
+            for (int i = lane; i < per; i += 32) probs[worst * per + i] = -1.0f;
+            __syncwarp();
+        }
     }
     float wsum = 0.0f, last = 0.0f, mine = 0.0f;
     for (int j = 0; j < k; ++j) {

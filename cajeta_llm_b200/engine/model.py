@@ -30,12 +30,16 @@ class Model:
         self.embedding_part = make_part("embedding", plan.embedding, "", runtime, vocab_size=self.vocab,
                                         hidden_size=self.hidden, weight_name=plan.embedding_name)
         self.blocks = [make_part("block", layer.block, layer.prefix, runtime, layer=layer) for layer in plan.layers]
+        # steps on the residual stream that run right before a schedule entry's layer
+        self.before = [make_part("stream", e.before, e.before_prefix, runtime) if e.before is not None else None
+                       for e in plan.schedule]
         self.final_norm = make_part("norm", plan.final_norm, plan.final_norm_prefix, runtime)
         self.head_part = make_part("head", plan.head, "", runtime, vocab_size=self.vocab, hidden_size=self.hidden,
                                    weight_name=plan.lm_head_name, embedding=self.embedding_part)
 
     def parts(self):
-        return [self.embedding_part] + list(self.blocks) + [self.final_norm, self.head_part]
+        return ([self.embedding_part] + list(self.blocks) + [b for b in self.before if b is not None]
+                + [self.final_norm, self.head_part])
 
     @property
     def embedding(self) -> Optional[torch.Tensor]:
@@ -75,8 +79,22 @@ class Model:
     def cache_from(self) -> List[Optional[int]]:
         return [e.cache_from for e in self.plan.schedule]
 
+    def named_state_needs(self) -> Dict[str, StateNeed]:
+        """Per-request state of parts that are not schedule entries: the embedding's, under ``"embedding"``."""
+        need = getattr(self.embedding_part, "state_need", lambda: None)()
+        return {"embedding": need} if need is not None else {}
+
+    @property
+    def keeps_embedding_output(self) -> bool:
+        """Whether a stream part of the plan reads the embedding's rows of the step again."""
+        parts = [b for b in self.before if b is not None] + [getattr(b, "after", None) for b in self.blocks]
+        return any(getattr(p, "needs_embedding_output", False) for p in parts if p is not None)
+
     # -- the pieces of a step outside the blocks -------------------------------------
-    def embed(self, token_ids: torch.Tensor) -> torch.Tensor:
+    def embed(self, token_ids: torch.Tensor, ctx=None, state: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """An embedding that keeps per-request state gets the step's context and its state tensor."""
+        if state is not None:
+            return self.embedding_part.forward(token_ids, ctx, state)
         return self.embedding_part.forward(token_ids)
 
     def logits(self, hs: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

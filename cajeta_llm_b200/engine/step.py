@@ -81,6 +81,8 @@ class StepContext:
     decode_scratch: Optional[object] = None    # scratch of the split-KV decode attention for this step (None: the runtime's)
     routing_pin: Optional[Dict[str, torch.Tensor]] = None     # a routed feed-forward's prefix -> int32 [rows, k]: experts given, not chosen
     routing_dump: Optional[Dict[str, tuple]] = None           # filled by routed feed-forwards: prefix -> (experts [rows, k], margins [rows])
+    routing_seen: Dict[str, int] = field(default_factory=dict)  # how often each routed feed-forward has run in this step
+    embedding_output: Optional[torch.Tensor] = None           # the embedding's rows of the step, kept when a stream part of the plan reads them
 
 
 @dataclass
@@ -137,7 +139,8 @@ class ModelRunner:
                 return max_seqs * whole
         self.max_step_tokens = max_step_tokens
         self.cache = CacheManager(model.kv_needs(), model.state_needs(), model.cache_from(), page_tokens, max_seqs,
-                                  max_tokens_per_seq, num_pages, self.runtime.cache_dtype, self.runtime.device)
+                                  max_tokens_per_seq, num_pages, self.runtime.cache_dtype, self.runtime.device,
+                                  named_state_needs=model.named_state_needs())
         self.page_tokens = page_tokens
         self.max_tokens_per_seq = max_tokens_per_seq
         self.steps_run = 0
@@ -268,8 +271,12 @@ class ModelRunner:
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
         """Embedding, every schedule entry, then final norm and head on the wanted rows."""
-        hs = self.model.embed(ctx.token_ids)
+        hs = self.model.embed(ctx.token_ids, ctx, self.cache.state.get("embedding"))
+        if self.model.keeps_embedding_output:
+            ctx.embedding_output = hs.clone()
         for i, e in enumerate(self.model.plan.schedule):
+            if self.model.before[i] is not None:
+                self.model.before[i].forward(hs, ctx)
             k_plane, v_plane, group = self.cache.plane(i)
             ectx = EntryContext(index=i, writes_cache=e.cache_from is None, k_plane=k_plane, v_plane=v_plane,
                                 block_table=ctx.tables[group] if group is not None else None,

@@ -13,6 +13,19 @@ projection is added into the residual stream (model/CausalLM.cajeta:1498,1506).
 Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``window``,
 ``qkv_bias``, ``out_bias``, ``scale``, ``position`` (a position PartSpec).
 
+Optional, each off by default (a mixer that sets any of them runs the general kernels:
+``head_prepare`` and the general paged attention):
+``value_dim``: the values' head size when it is not the keys';
+``softcap`` c > 0: a score becomes ``c tanh(s / c)`` after the scale;
+``qk_norm``: ``{"q": name, "k": name, "eps": e}``, an RMS norm over each head of q and of k with a
+weight of ``head_dim`` shared by the heads, before the rotation;
+``values_from_keys``: there is no value projection, a key as projected (before norm and rotation)
+is also the value;
+``head_gate``: a tensor name; ``W_g`` of ``[num_heads, hidden]`` reads the mixer's input and head
+``h``'s output is multiplied by ``sigmoid(W_g x)_h`` before the output projection;
+``names``: the tensor names of ``q``, ``k``, ``v``, ``o`` under the part's prefix.
+A position part's ``magnitude`` (a stretched rotation's) multiplies cos and sin.
+
 An entry that reads another entry's cache (``entry.writes_cache`` false) projects and
 rotates only q.
 """
@@ -42,6 +55,18 @@ class PagedAttention(Part):
         self.out_bias = bool(spec.get("out_bias", False))
         scale = spec.get("scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.value_dim = int(spec.get("value_dim", 0) or self.head_dim)
+        self.softcap = float(spec.get("softcap", 0.0) or 0.0)
+        self.qk_norm = dict(spec.get("qk_norm") or {}) or None
+        self.values_from_keys = bool(spec.get("values_from_keys", False))
+        self.head_gate = spec.get("head_gate") or None
+        names = dict(spec.get("names") or {})
+        self.n_proj = {n: self.name(names.get(n, f"{n}_proj.weight")) for n in ("q", "k", "v", "o")}
+        self.allow_pending = True          # a block that has no norm after the mixer sets this False
+        if self.values_from_keys and self.value_dim != self.head_dim:
+            raise ValueError("values_from_keys needs value_dim == head_dim")
+        if self.softcap < 0.0:
+            raise ValueError(f"softcap must be positive (or 0 for none), found {self.softcap}")
         if self.heads % self.kv_heads != 0:
             raise ValueError(f"num_heads {self.heads} is not a multiple of num_kv_heads {self.kv_heads}")
         if self.head_dim > 256:
@@ -49,6 +74,13 @@ class PagedAttention(Part):
         self.position = make_part("position", spec["position"], prefix, runtime)
         self.q_dim = self.heads * self.head_dim
         self.kv_dim = self.kv_heads * self.head_dim
+        self.v_dim = 0 if self.values_from_keys else self.kv_heads * self.value_dim
+        self.o_dim = self.heads * self.value_dim
+        self.general = bool(self.softcap > 0.0 or self.qk_norm or self.values_from_keys or self.head_gate
+                            or self.value_dim != self.head_dim or getattr(self.position, "magnitude", 1.0) != 1.0)
+        if self.general and (self.qkv_bias or self.out_bias):
+            raise ValueError("the general attention path is built without biases")
+        self.q_norm_w = self.k_norm_w = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
@@ -56,7 +88,7 @@ class PagedAttention(Part):
 
     # -- what the cache manager must provide ----------------------------------------
     def cache_need(self) -> Optional[KvNeed]:
-        return KvNeed(self.kv_heads, self.head_dim, self.window)
+        return KvNeed(self.kv_heads, self.head_dim, self.window, value_dim=0 if self.value_dim == self.head_dim else self.value_dim)
 
     def state_need(self):
         return None
@@ -64,11 +96,17 @@ class PagedAttention(Part):
     # -- tensors ---------------------------------------------------------------------
     def params(self) -> Dict[str, ParamSpec]:
         p = {
-            self.name("q_proj.weight"): ParamSpec((self.q_dim, self.hidden)),
-            self.name("k_proj.weight"): ParamSpec((self.kv_dim, self.hidden)),
-            self.name("v_proj.weight"): ParamSpec((self.kv_dim, self.hidden)),
-            self.name("o_proj.weight"): ParamSpec((self.hidden, self.q_dim)),
+            self.n_proj["q"]: ParamSpec((self.q_dim, self.hidden)),
+            self.n_proj["k"]: ParamSpec((self.kv_dim, self.hidden)),
+            self.n_proj["o"]: ParamSpec((self.hidden, self.o_dim)),
         }
+        if not self.values_from_keys:
+            p[self.n_proj["v"]] = ParamSpec((self.v_dim, self.hidden))
+        if self.qk_norm:
+            p[self.name(self.qk_norm["q"])] = ParamSpec((self.head_dim,), role="vector", init="ones")
+            p[self.name(self.qk_norm["k"])] = ParamSpec((self.head_dim,), role="vector", init="ones")
+        if self.head_gate:
+            p[self.name(self.head_gate)] = ParamSpec((self.heads, self.hidden))
         if self.qkv_bias:
             p[self.name("q_proj.bias")] = ParamSpec((self.q_dim,), role="vector")
             p[self.name("k_proj.bias")] = ParamSpec((self.kv_dim,), role="vector")
@@ -79,7 +117,9 @@ class PagedAttention(Part):
 
     def libraries(self) -> set:
         libs = {"rowwise", "gemm_simt"}
-        if self.runtime.fast_kernels and self.head_dim in (64, 128):
+        if self.general:
+            libs.add("attention_paged")
+        elif self.runtime.fast_kernels and self.head_dim in (64, 128):
             libs |= {"attention_decode", "attention_prefill_tc" if self.head_dim == 128 else "attention_prefill"}
         else:
             libs.add("attention_paged")
@@ -89,15 +129,23 @@ class PagedAttention(Part):
 
     def load(self, source) -> None:
         # q, k and v rows are stacked so that one product yields all three
-        self.w_qkv = torch.cat([self.fetch(source, self.name(f"{n}_proj.weight")) for n in ("q", "k", "v")], dim=0).contiguous()
+        rows = [self.fetch(source, self.n_proj[n]) for n in (("q", "k") if self.values_from_keys else ("q", "k", "v"))]
+        if self.head_gate:
+            rows.append(self.fetch(source, self.name(self.head_gate)))      # the gate's rows ride along: one product
+        self.w_qkv = torch.cat(rows, dim=0).contiguous()
+        if self.qk_norm:
+            self.q_norm_w = self.fetch(source, self.name(self.qk_norm["q"]))
+            self.k_norm_w = self.fetch(source, self.name(self.qk_norm["k"]))
         if self.qkv_bias:
             self.b_qkv = torch.cat([self.fetch(source, self.name(f"{n}_proj.bias")) for n in ("q", "k", "v")], dim=0).contiguous()
-        self.w_o = self.fetch(source, self.name("o_proj.weight"))
+        self.w_o = self.fetch(source, self.n_proj["o"])
         if self.out_bias:
             self.b_o = self.fetch(source, self.name("o_proj.bias"))
 
     # -- one step --------------------------------------------------------------------
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> Optional[torch.Tensor]:
+        if self.general:
+            return self._forward_general(x, residual, ctx, entry)
         rt = self.runtime
         T = x.shape[0]
         pos = self.position
@@ -131,8 +179,43 @@ class PagedAttention(Part):
             K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
                               entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale)
         K.tag = "o"
-        parts = project_split(rt, out.view(T, self.q_dim), self.w_o, bias=self.b_o)
+        parts = project_split(rt, out.view(T, self.q_dim), self.w_o, bias=self.b_o) if self.allow_pending else None
         if parts is None:
             project(rt, out.view(T, self.q_dim), self.w_o, residual, bias=self.b_o, accumulate=True)
         K.tag = None
         return parts                         # partial sums owed to the residual stream (the next norm adds them), or None
+
+    def _forward_general(self, x: torch.Tensor, residual: torch.Tensor, ctx, entry) -> Optional[torch.Tensor]:
+        """The path of a mixer with any of the optional parameters: one product for q | k | (v) | (gate), heads made
+        ready (norm, rotation, cache write), attention with capped scores and gated heads, output projection."""
+        rt = self.runtime
+        T = x.shape[0]
+        pos = self.position
+        write = entry.writes_cache
+        gate_cols = self.heads if self.head_gate else 0
+        if write:
+            w, k_off, v_off, g_off = self.w_qkv, self.q_dim, self.q_dim + self.kv_dim, self.q_dim + self.kv_dim + self.v_dim
+        else:
+            # an entry that reads another entry's cache projects q (and the gate) only
+            w = self.w_qkv[:self.q_dim] if not gate_cols else torch.cat([self.w_qkv[:self.q_dim], self.w_qkv[-gate_cols:]], dim=0)
+            k_off, v_off, g_off = 0, 0, self.q_dim
+        qkv = torch.empty((T, w.shape[0]), dtype=torch.float32, device=x.device)
+        K.tag = "qkv"
+        project(rt, x, w, qkv)
+        q = torch.empty((T, self.heads, self.head_dim), dtype=rt.act_dtype, device=x.device)
+        K.tag = "heads + cache write"
+        K.head_prepare(qkv, 0, k_off, -1 if self.values_from_keys else v_off, q, entry.k_plane, entry.v_plane, ctx.positions,
+                       ctx.row_req, entry.block_table, entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.value_dim,
+                       pos.rotary_dim, pos.inv_freq, getattr(pos, "magnitude", 1.0), self.q_norm_w, self.k_norm_w,
+                       float(self.qk_norm["eps"]) if self.qk_norm else 0.0, write)
+        out = torch.empty((T, self.heads, self.value_dim), dtype=rt.act_dtype, device=x.device)
+        K.tag = "attention"
+        K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens,
+                          self.heads, self.kv_heads, self.head_dim, self.window, self.scale, value_dim=self.value_dim,
+                          softcap=self.softcap, head_gate=qkv if gate_cols else None, gate_offset=g_off)
+        K.tag = "o"
+        parts = project_split(rt, out.view(T, self.o_dim), self.w_o) if self.allow_pending else None
+        if parts is None:
+            project(rt, out.view(T, self.o_dim), self.w_o, residual, accumulate=True)
+        K.tag = None
+        return parts

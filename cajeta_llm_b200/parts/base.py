@@ -15,6 +15,7 @@ Categories and what each must offer
 ``block``         ``forward(hs, ctx, entry)`` over its mixer, feed-forward and norms
 ``embedding``     ``forward(token_ids) -> float32 [T, hidden]``, ``table``
 ``head``          ``forward(x [rows, hidden]) -> float32 [rows, vocab]``
+``stream``        ``forward(hs, ctx) -> None``: a step on the residual stream between sublayers or layers
 
 ``x`` is the normed input in the activation dtype, ``residual`` the float32 residual
 stream the part adds its result into (the residual sum is always 32-bit; a mixer may
@@ -55,6 +56,7 @@ class Runtime:
         self.fast_kernels = fast_kernels and dtype == "bfloat16"
         self._decode_scratch = None
         self._sm_count = None
+        self.shared_tensors = {}      # tensors several parts read (a table cut up among the layers), by tensor name
 
     @property
     def sm_count(self) -> int:
@@ -99,12 +101,14 @@ class Runtime:
 class KvNeed:
     """A mixer that caches keys and values: pages of ``kv_heads x head_dim`` per token;
     ``window`` > 0 means only the last ``window`` positions are ever read.  ``values`` false:
-    one vector per token is all it caches (no plane of values is kept)."""
+    one vector per token is all it caches (no plane of values is kept).  ``value_dim``: the size
+    of a head's value when it is not ``head_dim`` (0 = the same)."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
     values: bool = True
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -150,9 +154,16 @@ class Part:
         spec = cache[name]
         return self.runtime.place(source.get(name, spec), spec)
 
+    def fetch_shared(self, source: Any, name: str) -> torch.Tensor:
+        """A tensor that several parts of the model read: loaded once, then found on the runtime."""
+        held = self.runtime.shared_tensors
+        if name not in held:
+            held[name] = self.fetch(source, name)
+        return held[name]
+
 
 _REGISTRY: Dict[Tuple[str, str], Type[Part]] = {}
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "stream")
 
 
 def register_part(category: str, kind: str, cls: Optional[Type[Part]] = None, replace: bool = False):

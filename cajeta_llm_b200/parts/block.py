@@ -12,6 +12,11 @@ feed-forward (``LayerSpec.feed_forward`` is None).  The sublayers see ``hs`` rou
 the activation dtype (a feed-forward that wants its input exactly gets the float32 stream
 itself); each adds its result into a zeroed float32 buffer of the stream's shape, which one
 kernel norms and adds.  Same parameters as ``prenorm``.
+
+``parallel``: one norm, both sublayers read its output: ``h = norm(hs); hs += mixer(h) + feed_forward(h)``
+(each adds its result into the float32 stream).  A layer may have no feed-forward.  After the
+sublayers the layer's ``stream_after`` part, when it has one, runs on the stream.  Parameters:
+``mixer_norm_name``, ``mixer_name``, ``feed_forward_name``, ``stream_after_name``.
 """
 from __future__ import annotations
 
@@ -126,3 +131,51 @@ class OutputNormBlock(Part):
         y = torch.zeros_like(hs)
         ff.forward(self._input(hs), hs if getattr(ff, "needs_f32_input", False) else None, y, ctx)
         self._add_normed(hs, y, None, self.feed_forward_norm)
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Part):
+    def __init__(self, spec, prefix, runtime, layer: LayerSpec):
+        super().__init__(spec, prefix, runtime)
+        self.mixer_norm = make_part("norm", layer.mixer_norm, self.name(spec["mixer_norm_name"]), runtime)
+        self.mixer = make_part("mixer", layer.mixer, self.name(spec["mixer_name"]), runtime)
+        # no norm follows the mixer inside this block: it adds its whole result itself
+        self.mixer.allow_pending = False
+        self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward = make_part("feed_forward", layer.feed_forward, self.name(spec["feed_forward_name"]), runtime)
+        self.after = None
+        if layer.stream_after is not None:
+            self.after = make_part("stream", layer.stream_after, self.name(spec.get("stream_after_name", "")), runtime)
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward, self.after) if p is not None)
+
+    def params(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for p in self.parts():
+            out.update(p.params())
+        return out
+
+    def libraries(self) -> set:
+        out = set()
+        for p in self.parts():
+            out |= p.libraries()
+        return out
+
+    def load(self, source) -> None:
+        for p in self.parts():
+            p.load(source)
+
+    def forward(self, hs: torch.Tensor, ctx, entry) -> None:
+        ff = self.feed_forward
+        wants_split = getattr(ff, "wants_split_input", None)
+        split = bool(wants_split and wants_split(hs.shape[0]))
+        x, x_exact = self.mixer_norm.forward(hs, want_f32=getattr(ff, "needs_f32_input", False) and not split, want_split=split)
+        pending = self.mixer.forward(x, hs, ctx, entry)
+        if pending is not None:
+            raise RuntimeError("a parallel block's mixer must add its result itself (it returned partial sums)")
+        if ff is not None:
+            ff.forward(x, x_exact, hs, ctx)
+        if self.after is not None:
+            self.after.forward(hs, ctx)

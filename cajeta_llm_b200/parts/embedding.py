@@ -6,6 +6,13 @@ float32 residual stream, times ``scale`` when one is given (the reference's
 Parameters: ``scale`` (optional).  Must offer ``forward(token_ids int32 [T]) -> float32
 [T, hidden]`` and ``table`` (the ``[vocab, hidden]`` tensor, which a tied head reads).
 
+``pair_hash_embedding`` (category ``embedding``): the token's row plus a row of a second table chosen by
+the pair (previous token, token): row ``(prev * mul_prev + token * mul_cur) mod buckets``, and the table's
+last row (number ``buckets``) for a request's first token.  The previous token of a request's first row of
+a step is per-request state (``state_need()``: one int32, the request's last token of the step before),
+which the cache manager keeps by slot; ``forward(token_ids, ctx, state)`` reads and updates it from the
+step's device metadata only.  Parameters: ``buckets``, ``mul_prev``, ``mul_cur``, ``pair_name``.
+
 ``linear_head`` (category ``head``): ``logits = x W^T (+ b)`` in float32 on the rows it is
 given (the final norm has already picked and normed the wanted rows:
 model/CausalLM.cajeta:1712-1718); ``W`` is the embedding table when the plan names no
@@ -53,6 +60,45 @@ class TokenEmbedding(Part):
         hs = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
         K.tag = "embedding"
         K.embed_gather(hs, self.table, token_ids, self.scale)
+        K.tag = None
+        return hs
+
+
+@register_part("embedding", "pair_hash_embedding")
+class PairHashEmbedding(TokenEmbedding):
+    def __init__(self, spec, prefix, runtime, vocab_size: int, hidden_size: int, weight_name: str):
+        super().__init__(spec, prefix, runtime, vocab_size, hidden_size, weight_name)
+        self.buckets = int(spec["buckets"])
+        self.mul_prev = int(spec["mul_prev"])
+        self.mul_cur = int(spec["mul_cur"])
+        self.pair_name = str(spec["pair_name"])
+        if self.buckets < 1 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError("pair_hash_embedding: buckets must be positive, the multipliers not negative")
+        self.pair = None
+
+    def state_need(self):
+        from .base import StateNeed
+        return StateNeed((1,), torch.int32)
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec((self.vocab, self.hidden)),
+                self.pair_name: ParamSpec((self.buckets + 1, self.hidden))}
+
+    def libraries(self) -> set:
+        return {"stream_ops"}
+
+    def load(self, source) -> None:
+        super().load(source)
+        self.pair = self.fetch(source, self.pair_name)
+
+    def forward(self, token_ids: torch.Tensor, ctx=None, state: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if ctx is None or state is None:
+            raise ValueError("pair_hash_embedding needs the step's context and its per-request state")
+        hs = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
+        K.tag = "embedding"
+        K.pair_embed(hs, self.table, self.pair, token_ids, ctx.positions, ctx.row_req, ctx.req_start, ctx.req_slot, state,
+                     self.buckets, self.mul_prev, self.mul_cur)
+        K.pair_commit(token_ids, ctx.req_start, ctx.req_slot, state, ctx.n_requests)
         K.tag = None
         return hs
 

@@ -25,7 +25,13 @@ sigma(l_e); the order of the experts is the same, the weights differ); ``weight_
 (``output``, the default: y = sum_j w_j expert_j(x); or ``input``: y = sum_j expert_j(w_j x),
 the weight multiplying the float32 row before it is rounded for the products);
 ``names`` (optional tensor-name templates under the part's prefix: ``router``, and
-``gate`` / ``up`` / ``down`` with ``{e}`` for the expert's index).
+``gate`` / ``up`` / ``down`` with ``{e}`` for the expert's index; ``shared_gate`` / ``shared_up`` /
+``shared_down`` and ``shared_sg``, the shared expert's tensors and its sigmoid gate);
+``act_limit`` L > 0 with ``act_alpha`` a: an expert is the capped form ``g = min(W_g x, L)``,
+``u = clamp(W_u x, -L, L)``, ``W_d (g sigmoid(a g) (u + 1))`` instead of SwiGLU; ``shared_act_limit`` /
+``shared_act_alpha``: the same for the shared expert (default: the experts');
+``route_groups`` ``(count, keep)``: the experts form ``count`` equal groups of neighbours, a group's
+score is its largest score, and only experts of the ``keep`` best groups can be picked.
 
 The file stores one tensor per expert and projection
 (``experts.{e}.gate_proj.weight`` ...); they are stacked into ``[E, I, H]`` and
@@ -106,6 +112,20 @@ class SparseMoE(Part):
         if self.weight_on not in ("output", "input"):
             raise ValueError(f"weight_on must be 'output' or 'input', found '{self.weight_on}'")
         names = dict(spec.get("names") or {})
+        self.act_limit = float(spec.get("act_limit", 0.0) or 0.0)
+        self.act_alpha = float(spec.get("act_alpha", 1.0))
+        self.shared_act_limit = float(spec.get("shared_act_limit", self.act_limit) or 0.0)
+        self.shared_act_alpha = float(spec.get("shared_act_alpha", self.act_alpha))
+        groups = spec.get("route_groups")
+        self.route_groups = (int(groups[0]), int(groups[1])) if groups and int(groups[0]) > 1 else None
+        if self.route_groups:
+            count, keep = self.route_groups
+            if self.num_experts % count != 0 or not 1 <= keep <= count:
+                raise ValueError(f"route_groups {self.route_groups}: {self.num_experts} experts must form equal groups, 1 <= keep <= count")
+            if keep * (self.num_experts // count) < self.top_k:
+                raise ValueError(f"route_groups {self.route_groups}: the kept groups hold fewer than top_k = {self.top_k} experts")
+        self.n_shared = {proj: self.name(names.get(f"shared_{proj}", f"shared_expert.{proj}_proj.weight")) for proj in ("gate", "up", "down")}
+        self.n_shared_sg = self.name(names.get("shared_sg", "shared_expert_gate.weight"))
         self.n_router = self.name(names.get("router", "gate.weight"))
         self.n_expert = {proj: names.get(proj, f"experts.{{e}}.{proj}_proj.weight") for proj in ("gate", "up", "down")}
         if not 1 <= self.top_k <= self.num_experts:
@@ -119,7 +139,8 @@ class SparseMoE(Part):
         self.router_split = None        # [cols, 3 hidden] bfloat16: router rows (and the gate's) three times over
         # chunks of the shared expert that run as extra groups of the grouped products
         self.shared_chunks = 0
-        if self.shared_inter > 0 and self.shared_inter % self.inter == 0 and self.shared_inter // self.inter <= 64:
+        same_act = (self.act_limit, self.act_alpha) == (self.shared_act_limit, self.shared_act_alpha)
+        if self.shared_inter > 0 and self.shared_inter % self.inter == 0 and self.shared_inter // self.inter <= 64 and same_act:
             self.shared_chunks = self.shared_inter // self.inter
 
     def params(self) -> Dict[str, ParamSpec]:
@@ -129,11 +150,11 @@ class SparseMoE(Part):
             p[self.expert_name("up", e)] = ParamSpec((self.inter, self.hidden))
             p[self.expert_name("down", e)] = ParamSpec((self.hidden, self.inter))
         if self.shared_inter > 0:
-            p[self.name("shared_expert.gate_proj.weight")] = ParamSpec((self.shared_inter, self.hidden))
-            p[self.name("shared_expert.up_proj.weight")] = ParamSpec((self.shared_inter, self.hidden))
-            p[self.name("shared_expert.down_proj.weight")] = ParamSpec((self.hidden, self.shared_inter))
+            p[self.n_shared["gate"]] = ParamSpec((self.shared_inter, self.hidden))
+            p[self.n_shared["up"]] = ParamSpec((self.shared_inter, self.hidden))
+            p[self.n_shared["down"]] = ParamSpec((self.hidden, self.shared_inter))
             if self.shared_gate:
-                p[self.name("shared_expert_gate.weight")] = ParamSpec((1, self.hidden), role="vector")
+                p[self.n_shared_sg] = ParamSpec((1, self.hidden), role="vector")
         return p
 
     def expert_name(self, proj: str, e: int) -> str:
@@ -161,9 +182,9 @@ class SparseMoE(Part):
         self.w_up = slab("up", I, self.hidden)
         self.w_down = slab("down", self.hidden, I)
         if self.shared_inter > 0:
-            ws_gate = self.fetch(source, self.name("shared_expert.gate_proj.weight"))
-            ws_up = self.fetch(source, self.name("shared_expert.up_proj.weight"))
-            ws_down = self.fetch(source, self.name("shared_expert.down_proj.weight"))
+            ws_gate = self.fetch(source, self.n_shared["gate"])
+            ws_up = self.fetch(source, self.n_shared["up"])
+            ws_down = self.fetch(source, self.n_shared["down"])
             if C > 0:
                 # chunk c of the shared expert: rows [c I, (c + 1) I) of gate and up, columns of down
                 self.w_gate[E:].copy_(ws_gate.view(C, I, self.hidden))
@@ -177,7 +198,7 @@ class SparseMoE(Part):
             else:
                 self.ws_gate, self.ws_up, self.ws_down = ws_gate, ws_up, ws_down
             if self.shared_gate:
-                self.shared_gate_w = self.fetch(source, self.name("shared_expert_gate.weight")).reshape(-1).contiguous()
+                self.shared_gate_w = self.fetch(source, self.n_shared_sg).reshape(-1).contiguous()
 
         self._prepare_split_router()
 
@@ -231,10 +252,10 @@ class SparseMoE(Part):
             K.gemm_tc(x_exact, self.router_split, logits if splits > 1 else logits[0], K.EPI_STORE_F32, False, 128,
                       k_splits=splits)
             K.router_select(logits, self.num_experts, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap,
-                            sigmoid_scores=self.score == "sigmoid")
+                            sigmoid_scores=self.score == "sigmoid", groups=self.route_groups)
         else:
             K.router_topk(x_exact, self.router, self.shared_gate_w, k, self.norm_topk, sel, wts, shared_scale, pin=pin, gap=gap,
-                          sigmoid_scores=self.score == "sigmoid")
+                          sigmoid_scores=self.score == "sigmoid", groups=self.route_groups)
 
     def forward(self, x: torch.Tensor, x_exact: torch.Tensor, residual: torch.Tensor, ctx) -> None:
         rt = self.runtime
@@ -248,12 +269,20 @@ class SparseMoE(Part):
         # prefix -> int32 [rows, k]; the weights stay the rows' own probabilities), or ask for what was
         # picked and how narrowly (``ctx.routing_dump``: prefix -> (experts, margins))
         pins, dump = getattr(ctx, "routing_pin", None), getattr(ctx, "routing_dump", None)
-        pin = pins.get(self.prefix) if pins else None
+        # a layer that runs several times a step (a looped stretch) is '<prefix>' the first time and
+        # '<prefix>#1', '<prefix>#2', ... after that, in both dictionaries
+        key = self.prefix
+        if pins is not None or dump is not None:
+            seen = ctx.routing_seen.get(self.prefix, 0)
+            ctx.routing_seen[self.prefix] = seen + 1
+            if seen:
+                key = f"{self.prefix}#{seen}"
+        pin = pins.get(key) if pins else None
         gap = torch.empty((T,), dtype=torch.float32, device=dev) if dump is not None and pin is None else None
         K.tag = "router"
         self._route(x_exact, sel, wts, shared_scale, pin, gap)
         if dump is not None:
-            dump[self.prefix] = (sel, gap)
+            dump[key] = (sel, gap)
 
         shared_dense = self.ws_down is not None and self.shared_chunks > 0 and T >= self.SHARED_DENSE_MIN_ROWS
         C = 0 if shared_dense else self.shared_chunks
@@ -276,12 +305,12 @@ class SparseMoE(Part):
             K.scale_rows_gather(x_exact, slot_of_pick, wts, k, scaled)
             K.tag = "experts gate/up"
             project(rt, scaled, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, max_group_rows=T,
-                    offsets_settled=True)
+                    offsets_settled=True, act_limit=self.act_limit, act_alpha=self.act_alpha)
             wts = torch.ones_like(wts)
         else:
             K.tag = "experts gate/up"
             project(rt, x, self.w_gate[:G], act, w_up=self.w_up[:G], group_offsets=offsets, a_row_index=slot_token,
-                    max_group_rows=T)
+                    max_group_rows=T, act_limit=self.act_limit, act_alpha=self.act_alpha)
         y = torch.empty((n_slots, self.hidden), dtype=torch.float32, device=dev)
         K.tag = "experts down"
         project(rt, act, self.w_down[:G], y, group_offsets=offsets, max_group_rows=T, offsets_settled=True)
@@ -297,7 +326,7 @@ class SparseMoE(Part):
             else:
                 ws_gate, ws_up = self.ws_gate, self.ws_up
             K.tag = "shared gate/up"
-            project(rt, x, ws_gate, sact, w_up=ws_up)
+            project(rt, x, ws_gate, sact, w_up=ws_up, act_limit=self.shared_act_limit, act_alpha=self.shared_act_alpha)
             shared = torch.empty((T, self.hidden), dtype=torch.float32, device=dev)
             K.tag = "shared down"
             project(rt, sact, self.ws_down, shared)

@@ -3,7 +3,9 @@
 ``ss = sum x_i^2; scale = 1 / sqrt(ss / dim + eps); y_i = x_i * scale * w_i`` with the
 statistics in float32 (model/Prim.cajeta:120-151; weight and eps held per norm,
 model/RMSNorm.cajeta:14-53).  Parameters: ``dim``, ``eps``, ``weight_name`` (the weight's
-tensor name under the part's prefix, default ``weight``; empty: the prefix itself).
+tensor name under the part's prefix, default ``weight``; empty: the prefix itself), ``offset``
+(optional: the stored weight lies around zero and ``offset + w`` multiplies, so 1 for a ``1 + w`` norm;
+the sum is formed once at load, in float32).
 """
 from __future__ import annotations
 
@@ -23,16 +25,19 @@ class RMSNorm(Part):
         self.dim = int(spec["dim"])
         self.eps = float(spec["eps"])
         self.weight_name = self.name(spec.get("weight_name", "weight"))
+        self.offset = float(spec.get("offset", 0.0) or 0.0)
         self.weight: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {self.weight_name: ParamSpec((self.dim,), role="vector", init="ones")}
+        return {self.weight_name: ParamSpec((self.dim,), role="vector", init="normal" if self.offset else "ones")}
 
     def libraries(self) -> set:
         return {"rowwise"}
 
     def load(self, source) -> None:
         self.weight = self.fetch(source, self.weight_name)
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def forward(self, x: torch.Tensor, want_f32: bool = False, row_index: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None, pending: Optional[torch.Tensor] = None,

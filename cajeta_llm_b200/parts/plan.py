@@ -71,6 +71,7 @@ class LayerSpec:
     feed_forward: Optional[PartSpec]          # None: the layer has no feed-forward (a block kind must allow it)
     mixer_norm: PartSpec
     feed_forward_norm: Optional[PartSpec]
+    stream_after: Optional[PartSpec] = None   # a step on the residual stream after the layer's sublayers (a block kind must run it)
 
 
 @dataclass(frozen=True)
@@ -80,11 +81,15 @@ class ScheduleEntry:
     ``layer`` indexes ``ModelPlan.layers``.  ``cache_from`` is None when the entry
     owns a cache plane (it writes keys and values and reads them); otherwise it is
     the index of an earlier schedule entry whose plane this entry reads without
-    writing.
+    writing.  ``before`` is a step on the residual stream (a ``stream`` part, under the tensor-name
+    prefix ``before_prefix``) that runs right before the entry's layer: the start of a pass over a
+    stretch of layers, for one.
     """
 
     layer: int
     cache_from: Optional[int] = None
+    before: Optional[PartSpec] = None
+    before_prefix: str = ""
 
 
 @dataclass(frozen=True)

@@ -8,9 +8,17 @@ row's absolute position, with the angle ``float32(p) * inv_freq[d]`` computed in
 
 ``rope``: ``inv_freq[d] = theta^(-2d / rotary_dim)`` computed in float32 as the
 reference does (model/Prim.cajeta:1866-1880; per-layer state, model/Attention.cajeta:72-99).
+``scaling`` (optional, on ``rope``) stretches the slow frequencies (the YaRN form): with
+``c(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta)``, ``lo = max(floor(c(fast)), 0)``,
+``hi = min(ceil(c(slow)), rotary_dim - 1)`` and ``ramp_d = clamp((d - lo) / max(hi - lo, 0.001), 0, 1)``
+the frequency is ``f_d / factor * ramp_d + f_d (1 - ramp_d)``, and the part offers ``magnitude`` =
+``0.1 ln(factor) + 1``, by which a mixer multiplies cos and sin (1 without scaling).  The table is worked
+out in float64 and rounded once.
 ``none``: no rotation.
 """
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -31,6 +39,23 @@ class RotaryEncoding(Part):
         d = np.arange(half, dtype=np.float32)
         exponent = (np.float32(0.0) - np.float32(2.0) * d) / np.float32(self.rotary_dim)
         inv = np.power(np.float32(self.theta), exponent).astype(np.float32)
+        self.magnitude = 1.0
+        scaling = spec.get("scaling")
+        if scaling:
+            factor, original = float(scaling["factor"]), float(scaling["original"])
+            if factor <= 0.0 or original <= 0.0 or self.theta <= 1.0:
+                raise ValueError("rope scaling needs a positive factor and original length and theta > 1")
+
+            def turns_dim(turns: float) -> float:
+                return self.rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(turns_dim(float(scaling["fast"]))), 0)
+            hi = min(math.ceil(turns_dim(float(scaling["slow"]))), self.rotary_dim - 1)
+            i = np.arange(half, dtype=np.float64)
+            f = np.power(float(self.theta), -2.0 * i / self.rotary_dim)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            inv = (f / factor * ramp + f * (1.0 - ramp)).astype(np.float32)
+            self.magnitude = 0.1 * math.log(factor) + 1.0
         self.inv_freq = torch.from_numpy(inv).to(runtime.device)
 
 
@@ -40,3 +65,4 @@ class NoPosition(Part):
         super().__init__(spec, prefix, runtime)
         self.rotary_dim = 0
         self.inv_freq = None
+        self.magnitude = 1.0
