@@ -1,7 +1,7 @@
-"""Throughput of a Balalorn model at layer sizes that resemble real models', beside the
+"""Throughput of a Balalorn or a Saropel model at layer sizes that resemble real models', beside the
 engine's Qwen2-MoE model at equal width, depth, experts and feed-forward sizes.
 
-``python bench.py --design balalorn [--sizes small,medium,large]`` prints one JSON line per
+``python bench.py --design balalorn|saropel [--sizes small,medium,large]`` prints one JSON line per
 (size, model): prefill tokens a second (one prompt of 2,048 tokens), decode tokens a second
 (8 requests of 512 tokens each, steps replayed from CUDA graphs), and where the time of both
 steps goes by class of work (launches serialised, an event behind each), with the bytes or
@@ -39,12 +39,33 @@ def balalorn_config(s):
             "layers": [kinds[i % 4](i) for i in range(s["layers"])]}
 
 
-def qwen_config(s):
+SAROPEL_WINDOWS = (1024, 4096)      # of the capped layers and of the rotated, gated ones
+
+
+def saropel_config(s):
+    """Three layers of weights, four layer runs (the middle layer runs twice, as a looped stretch): capped
+    windowed attention + dense, rotated gated attention (values = keys) + routed with a shared expert, capped + dense."""
+    h, H = s["width"], s["heads"]
+    capped = {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": SAROPEL_WINDOWS[0]}}
+    rotated = {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": SAROPEL_WINDOWS[1]},
+               "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"], "limit": 7.0},
+           "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": s["eff"], "limit": 7.0}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    return {"architecture": "Saropel", "width": h, "vocab": VOCAB, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 7}}, "token_side": {"dim": 256},
+            "loop": {"start": 1, "stop": 2, "times": 2},
+            "layers": [{"type": "attention", "mixer": capped, "mlp": dense}, {"type": "attention_2", "mixer": rotated, "mlp": moe},
+                       {"type": "attention", "mixer": capped, "mlp": dense}]}
+
+
+def qwen_config(s, shared=0):
     return {"architectures": ["Qwen2MoeForCausalLM"], "hidden_size": s["width"], "intermediate_size": s["ff"],
             "num_hidden_layers": s["layers"], "num_attention_heads": s["heads"], "num_key_value_heads": s["heads"], "head_dim": 128,
             "vocab_size": VOCAB, "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
             "num_experts": s["experts"], "num_experts_per_tok": s["top"], "moe_intermediate_size": s["eff"],
-            "shared_expert_intermediate_size": 0, "norm_topk_prob": False, "decoder_sparse_step": 2, "mlp_only_layers": [],
+            "shared_expert_intermediate_size": shared, "norm_topk_prob": False, "decoder_sparse_step": 2, "mlp_only_layers": [],
             "tie_word_embeddings": False, "use_sliding_window": False}
 
 
@@ -54,6 +75,15 @@ def needs(design, s, rows, ctx, prefill):
     if design == "qwen2_moe":
         kv = ctx * 2 * H * 128 * 2
         out["attention"] = (rows * kv * L if not prefill else 0, 4 * H * 128 * rows * (rows + 1) // 2 * L if prefill else 0)
+        return out
+    if design == "saropel":
+        by = fl = 0
+        for w in (SAROPEL_WINDOWS[0], SAROPEL_WINDOWS[1], SAROPEL_WINDOWS[1], SAROPEL_WINDOWS[0]):      # the four layer runs
+            if prefill:
+                fl += 4 * H * 128 * sum(min(i + 1, w) for i in range(rows))
+            else:
+                by += rows * min(ctx, w) * 2 * H * 128 * 2
+        out["attention"] = (by, fl)
         return out
     n_lat, n_ssd, n_delta = (L + 3) // 4 + L // 4, (L + 2) // 4, (L + 1) // 4
     width = s["rank"] + 64
@@ -82,7 +112,9 @@ def run(args, peaks) -> int:
     rng = np.random.default_rng(3)
     for size in [x for x in args.sizes.split(",") if x]:
         s = SIZES[size]
-        for design, cfg in (("balalorn", balalorn_config(s)), ("qwen2_moe", qwen_config(s))):
+        pair = ((("saropel", saropel_config(s)), ("qwen2_moe", qwen_config(s, shared=s["eff"]))) if args.design == "saropel"
+                else (("balalorn", balalorn_config(s)), ("qwen2_moe", qwen_config(s))))
+        for design, cfg in pair:
             tokens = BATCH * (PROMPT + 128) + PREFILL + 64
             eng = LlmEngine.load(EngineOptions(config=cfg, random_weights=True, seed=11, dtype="bfloat16", ctx=PREFILL + 64, max_seqs=BATCH,
                                                block_tokens=16, num_blocks=-(-tokens // 16) + BATCH, max_batch_tokens=8192, warmup=False))

@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ positions, const int* __restrict__ row_req,
     const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int head_batches,
     int window, float scale, float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
-    int max_splits, int merge_later) {
+    int max_splits, int merge_later, float softcap, const float* __restrict__ head_gate, int gate_ld) {
     cj::release_successor();
     constexpr int COLS = HD / 8;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -418,7 +418,9 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const bool in = warp * 32 + kb * 16 + j * 8 + 2 * t4 + e < count;
-                s[kb][j][e] = in ? s[kb][j][e] * scale : -INFINITY;
+                // a capped score: cap * tanh(s / cap) after the scale
+                const float sv = softcap > 0.0f ? softcap * tanhf(s[kb][j][e] * scale / softcap) : s[kb][j][e] * scale;
+                s[kb][j][e] = in ? sv : -INFINITY;
                 mx0 = fmaxf(mx0, s[kb][j][e]);
             }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -489,6 +491,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
         const int h = h0 + row;
         if (n_splits == 1) {
             float inv = 1.0f / l;
+            if (head_gate) inv *= 1.0f / (1.0f + expf(-head_gate[(size_t)t * gate_ld + h]));
             *(__nv_bfloat162*)(out + ((size_t)t * n_heads + h) * HD + 2 * d2) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
         } else {
             size_t slot = ((size_t)t * n_heads + h) * max_splits + split;
@@ -534,6 +537,7 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
             a.y = fmaf(v.y, f, a.y);
         }
         float inv = 1.0f / L;
+        if (head_gate) inv *= 1.0f / (1.0f + expf(-head_gate[(size_t)t * gate_ld + h]));
         *(__nv_bfloat162*)(out + ((size_t)t * n_heads + h) * HD + 2 * d2) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
     }
 }
@@ -544,7 +548,8 @@ __global__ void __launch_bounds__(TC_THREADS, TC_BLOCKS) decode_attention_tc_ker
 template <int HD>
 __global__ void __launch_bounds__(128) decode_merge_kernel(
     __nv_bfloat16* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-    const int* __restrict__ positions, int T, int n_heads, int window, int max_splits) {
+    const int* __restrict__ positions, int T, int n_heads, int window, int max_splits, const float* __restrict__ head_gate,
+    int gate_ld) {
     cj::release_successor();
     const int lane = threadIdx.x & 31;
     const long long idx = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -563,6 +568,7 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(
     const size_t slot0 = (size_t)idx * max_splits;
     float M = -INFINITY;
     for (int sidx = 0; sidx < n_splits; ++sidx) M = fmaxf(M, part_ml[(slot0 + sidx) * 2]);
+    const float gate = head_gate ? 1.0f / (1.0f + expf(-head_gate[(size_t)(idx / n_heads) * gate_ld + (int)(idx % n_heads)])) : 1.0f;
     for (int d2 = lane; d2 < HD / 2; d2 += 32) {
         float L = 0.0f;
         float2 a = make_float2(0.0f, 0.0f);
@@ -573,7 +579,7 @@ __global__ void __launch_bounds__(128) decode_merge_kernel(
             a.x = fmaf(v.x, f, a.x);
             a.y = fmaf(v.y, f, a.y);
         }
-        float inv = 1.0f / L;
+        float inv = gate / L;
         *(__nv_bfloat162*)(out + (size_t)idx * HD + 2 * d2) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
     }
 }
@@ -626,7 +632,7 @@ CJ_EXPORT int cj_decode_attention_tc(const void* q, void* out, const void* kplan
                                      const int* row_req, const int* table, int table_stride, int page_tokens, int T,
                                      int n_heads, int n_kv, int hd, int window, float scale, int max_context,
                                      float* part_acc, float* part_ml, int* counters, int max_splits, int merge_later,
-                                     cudaStream_t stream) {
+                                     float softcap, const float* head_gate, int gate_ld, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !positions || !row_req || !table || !part_acc || !part_ml || !counters) return CJ_ERR_ARG;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0) return CJ_ERR_SIZE;
@@ -651,10 +657,11 @@ CJ_EXPORT int cj_decode_attention_tc(const void* q, void* out, const void* kplan
         cj::launch(decode_attention_tc_kernel<HD>, dim3(grid), dim3(TC_THREADS), smem, stream, (const __nv_bfloat16*)q, \
             (__nv_bfloat16*)out, (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane, positions, row_req, table, \
             table_stride, page_tokens, n_heads, n_kv, head_batches, window, scale, part_acc, part_ml, counters,        \
-            max_splits, merge_later && splits > 1 ? 1 : 0);                                                            \
+            max_splits, merge_later && splits > 1 ? 1 : 0, softcap, head_gate, gate_ld);                               \
         if (merge_later && splits > 1)                                                                                 \
             cj::launch(decode_merge_kernel<HD>, dim3((unsigned)(((long long)T * n_heads + 3) / 4)), dim3(128), 0, stream, \
-                (__nv_bfloat16*)out, (const float*)part_acc, (const float*)part_ml, positions, T, n_heads, window, max_splits); \
+                (__nv_bfloat16*)out, (const float*)part_acc, (const float*)part_ml, positions, T, n_heads, window, max_splits, \
+                head_gate, gate_ld);                                                                                   \
     }
     if (hd == 128) LAUNCH(128) else LAUNCH(64)
 #undef LAUNCH

@@ -6,7 +6,9 @@
 //
 // Per row at position p: keys [from, p], from = p + 1 - w when a window is set and
 // exceeded, else 0; s = (q . k) * scale; softmax with the running maximum subtracted;
-// o = (sum e v) / (sum e)  (model/PagedKvCache.cajeta:374-470).  The reference's
+// o = (sum e v) / (sum e)  (model/PagedKvCache.cajeta:374-470).  Optionally a score is capped,
+// s <- cap * tanh(s / cap) after the scale, and a head's output is multiplied by the sigmoid of a
+// gate value of its own (float32, one per row and head).  The reference's
 // counterpart is its query-tiled flash prefill over the page table
 // (model/AttnKernel.cajeta:2903).
 //
@@ -47,7 +49,8 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *(unsigned*)&v;
 }
 
-// element (row, col) of a [rows][HD] bf16 tile whose 16-byte chunks are XOR-swizzled by row
+// element (row, col) of a [rows][HD] bf16 tile whose 16-byte chunks are XOR-swizzled by row (HD here is
+// the tile's row stride, a power of two of at least 64: a head size of 96 lives in rows of 128)
 template <int HD>
 __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row, int col) {
     int chunk = (col >> 3) ^ (row & 7);
@@ -57,18 +60,20 @@ __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row,
 // HD: head size; BM: query rows a block; BN: keys a tile; MT: 16-row tiles a warp owns.  A
 // warp that owns two row tiles uses every key/value fragment it reads from shared memory
 // twice, which is what the legacy tensor path needs to stay ahead of shared-memory bandwidth.
-template <int HD, int BM, int BN, int MT>
+template <int HD, int HS, int BM, int BN, int MT>
 __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ kplane,
     const __nv_bfloat16* __restrict__ vplane, const int* __restrict__ req_start, const int* __restrict__ req_prior,
     int n_requests, const int* __restrict__ table, int table_stride, int page_tokens, int n_heads, int n_kv, int window,
-    float scale_log2) {
+    float scale, float softcap, const float* __restrict__ head_gate, int gate_ld) {
     cj::after_predecessor();
     cj::release_successor();
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [BM][HD]
-    __nv_bfloat16* ks = qs + BM * HD;                             // [2][BN][HD]
-    __nv_bfloat16* vs = ks + 2 * BN * HD;                         // [2][BN][HD]
+    __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [BM][HS]
+    __nv_bfloat16* ks = qs + BM * HS;                             // [2][BN][HS]
+    __nv_bfloat16* vs = ks + 2 * BN * HS;                         // [2][BN][HS]
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const float cap_log2 = softcap * 1.4426950408889634f, in_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     constexpr int CH = HD / 8;                                    // 16-byte chunks per row
     constexpr int THREADS = BM / (16 * MT) * 32;
 
@@ -98,8 +103,8 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
 
     // ---- loads -----------------------------------------------------------------------------
     auto load_kv = [&](int kt, int buf) {
-        __nv_bfloat16* kd = ks + buf * BN * HD;
-        __nv_bfloat16* vd = vs + buf * BN * HD;
+        __nv_bfloat16* kd = ks + buf * BN * HS;
+        __nv_bfloat16* vd = vs + buf * BN * HS;
         for (int i = tid; i < BN * CH; i += THREADS) {
             int r = i / CH, c = i % CH;
             int key = kt * BN + r;
@@ -111,15 +116,15 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
                 off = (((long long)(valid ? page : 0) * n_kv + kvh) * page_tokens + key % page_tokens) * HD + c * 8;
             }
             int pc = c ^ (r & 7);
-            cp_async16(kd + r * HD + pc * 8, kplane + off, valid);
-            cp_async16(vd + r * HD + pc * 8, vplane + off, valid);
+            cp_async16(kd + r * HS + pc * 8, kplane + off, valid);
+            cp_async16(vd + r * HS + pc * 8, vplane + off, valid);
         }
     };
     for (int i = tid; i < BM * CH; i += THREADS) {
         int r = i / CH, c = i % CH;
         bool valid = r < rows;
         const __nv_bfloat16* src = q + ((size_t)(row0 + (valid ? r : 0)) * n_heads + h) * HD + c * 8;
-        cp_async16(qs + r * HD + (c ^ (r & 7)) * 8, src, valid);
+        cp_async16(qs + r * HS + (c ^ (r & 7)) * 8, src, valid);
     }
     load_kv(kt_begin, 0);
     cp_async_commit();
@@ -143,8 +148,8 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        const __nv_bfloat16* kb = ks + buf * BN * HD;
-        const __nv_bfloat16* vb = vs + buf * BN * HD;
+        const __nv_bfloat16* kb = ks + buf * BN * HS;
+        const __nv_bfloat16* vb = vs + buf * BN * HS;
 
         // scores of MT x 16 rows x BN keys; the query fragments come from shared memory
         float s[MT][BN / 8][4];
@@ -157,12 +162,12 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
             unsigned qf[MT][4];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
-                ldmatrix_x4(qf[mt], tile_ptr<HD>(qs, wrow + mt * 16 + (lane & 15), kk * 16 + (lane >> 4) * 8));
+                ldmatrix_x4(qf[mt], tile_ptr<HS>(qs, wrow + mt * 16 + (lane & 15), kk * 16 + (lane >> 4) * 8));
 #pragma unroll
             for (int jp = 0; jp < BN / 16; ++jp) {
                 unsigned b[4];
                 int mi = lane >> 3;
-                ldmatrix_x4(b, tile_ptr<HD>((__nv_bfloat16*)kb, jp * 16 + (mi >> 1) * 8 + (lane & 7), kk * 16 + (mi & 1) * 8));
+                ldmatrix_x4(b, tile_ptr<HS>((__nv_bfloat16*)kb, jp * 16 + (mi >> 1) * 8 + (lane & 7), kk * 16 + (mi & 1) * 8));
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     mma_bf16(s[mt][2 * jp], qf[mt], b[0], b[1]);
@@ -184,8 +189,13 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     int key = kbase + j * 8 + 2 * t4 + e;
-                    float a = (key <= pos0 && key >= from0) ? s[mt][j][e] * scale_log2 : -INFINITY;
-                    float b = (key <= pos1 && key >= from1) ? s[mt][j][2 + e] * scale_log2 : -INFINITY;
+                    float a = s[mt][j][e] * scale_log2, b = s[mt][j][2 + e] * scale_log2;
+                    if (softcap > 0.0f) {
+                        a = cap_log2 * tanhf(s[mt][j][e] * in_cap);
+                        b = cap_log2 * tanhf(s[mt][j][2 + e] * in_cap);
+                    }
+                    if (!(key <= pos0 && key >= from0)) a = -INFINITY;
+                    if (!(key <= pos1 && key >= from1)) b = -INFINITY;
                     s[mt][j][e] = a;
                     s[mt][j][2 + e] = b;
                     mx0 = fmaxf(mx0, a);
@@ -227,7 +237,7 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
             for (int dp = 0; dp < HD / 16; ++dp) {
                 unsigned b[4];
                 int mi = lane >> 3;
-                ldmatrix_x4_trans(b, tile_ptr<HD>((__nv_bfloat16*)vb, kk * 16 + (mi & 1) * 8 + (lane & 7), dp * 16 + (mi >> 1) * 8));
+                ldmatrix_x4_trans(b, tile_ptr<HS>((__nv_bfloat16*)vb, kk * 16 + (mi & 1) * 8 + (lane & 7), dp * 16 + (mi >> 1) * 8));
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     mma_bf16(o[mt][2 * dp], pf[mt][kk], b[0], b[1]);
@@ -246,8 +256,12 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
         l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
         l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-        const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+        float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
         const int r0 = wrow + mt * 16 + g, r1 = r0 + 8;
+        if (head_gate) {
+            if (r0 < rows) i0 *= 1.0f / (1.0f + expf(-head_gate[(size_t)(row0 + r0) * gate_ld + h]));
+            if (r1 < rows) i1 *= 1.0f / (1.0f + expf(-head_gate[(size_t)(row0 + r1) * gate_ld + h]));
+        }
 #pragma unroll
         for (int i = 0; i < HD / 8; ++i) {
             int col = i * 8 + 2 * t4;
@@ -261,34 +275,37 @@ __global__ void __launch_bounds__(BM / (16 * MT) * 32) prefill_attention_kernel(
 
 // q, out: [T, n_heads, hd] bf16; planes [pages, n_kv, page_tokens, hd] bf16; req_start
 // [n_requests + 1], req_prior [n_requests] as the step function lays them out.  hd must be
-// 64 or 128.  block_rows: 64 or 128 query rows a block, 0 = chosen from the step's shape.
+// 32, 64, 96 or 128.  block_rows: 64 or 128 query rows a block, 0 = chosen from the step's shape.  softcap 0: none.
+// head_gate: null, or float32 with row stride gate_ld whose entry [t, h] gates head h of row t.
 CJ_EXPORT int cj_prefill_attention(const void* q, void* out, const void* kplane, const void* vplane, const int* req_start,
                                    const int* req_prior, int n_requests, int total_rows, const int* table, int table_stride,
                                    int page_tokens, int n_heads, int n_kv, int hd, int window, float scale,
-                                   int block_rows, cudaStream_t stream) {
+                                   int block_rows, float softcap, const float* head_gate, int gate_ld, cudaStream_t stream) {
     if (total_rows <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !req_start || !req_prior || !table) return CJ_ERR_ARG;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv != 0 || page_tokens <= 0 || n_heads > 65535) return CJ_ERR_SIZE;
-    if (hd != 64 && hd != 128) return CJ_ERR_SIZE;
-    float scale_log2 = scale * 1.4426950408889634f;
+    if (hd != 32 && hd != 64 && hd != 96 && hd != 128) return CJ_ERR_SIZE;
     // long portions: 128 query rows a block, every warp two row tiles; short ones: 64 rows, one tile a warp
     const int bm = (block_rows == 128 || (block_rows == 0 && total_rows >= 128 * n_requests)) ? 128 : 64;
-#define LAUNCH(HD, BM, BN, MT)                                                                                          \
+#define LAUNCH(HD, HS, BM, BN, MT)                                                                                      \
     {                                                                                                                   \
         dim3 grid((total_rows + BM - 1) / BM + n_requests, n_heads);                                                    \
-        size_t smem = (size_t)(BM + 4 * BN) * HD * sizeof(__nv_bfloat16);                                               \
+        size_t smem = (size_t)(BM + 4 * BN) * HS * sizeof(__nv_bfloat16);                                               \
         static bool configured = false;                                                                                 \
         if (!configured) {                                                                                              \
-            cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD, BM, BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD, HS, BM, BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                                        \
             configured = true;                                                                                          \
         }                                                                                                               \
-        cj::launch(prefill_attention_kernel<HD, BM, BN, MT>, dim3(grid), dim3(BM / (16 * MT) * 32), smem, stream,                           \
+        cj::launch(prefill_attention_kernel<HD, HS, BM, BN, MT>, dim3(grid), dim3(BM / (16 * MT) * 32), smem, stream,                           \
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kplane, (const __nv_bfloat16*)vplane,   \
-            req_start, req_prior, n_requests, table, table_stride, page_tokens, n_heads, n_kv, window, scale_log2);     \
+            req_start, req_prior, n_requests, table, table_stride, page_tokens, n_heads, n_kv, window, scale, softcap,  \
+            head_gate, gate_ld);                                                                                        \
     }
-    if (hd == 128) { if (bm == 128) LAUNCH(128, 128, 32, 2) else LAUNCH(128, 64, 64, 1) }
-    else { if (bm == 128) LAUNCH(64, 128, 64, 2) else LAUNCH(64, 64, 64, 1) }
+    if (hd == 128) { if (bm == 128) LAUNCH(128, 128, 128, 32, 2) else LAUNCH(128, 128, 64, 64, 1) }
+    else if (hd == 96) { if (bm == 128) LAUNCH(96, 128, 128, 32, 2) else LAUNCH(96, 128, 64, 64, 1) }
+    else if (hd == 64) { if (bm == 128) LAUNCH(64, 64, 128, 64, 2) else LAUNCH(64, 64, 64, 64, 1) }
+    else { if (bm == 128) LAUNCH(32, 64, 128, 64, 2) else LAUNCH(32, 64, 64, 64, 1) }
 #undef LAUNCH
     return launch_status();
 }

@@ -136,6 +136,17 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
+// cap log2(e) tanh(x) - sub for a raw score s with x = s scale / cap; tanh(x) = 1 - 2 / (e^2x + 1) from
+// the fast exponential and reciprocal (absolute error of a few 2^-23: a capped score is exact to the
+// grade of the uncapped form's single rounding); a masked score (-inf) stays -inf
+__device__ __forceinline__ float capped_score(float s, float in_cap, float cap_log2, float neg_sub) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(s * in_cap * 2.8853900817779268f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    const float y = fmaf(fmaf(-2.0f, r, 1.0f), cap_log2, neg_sub);
+    return s == -INFINITY ? -INFINITY : y;
+}
+
 __device__ __forceinline__ float ex2(float x) {       // 2^x, 0 for -inf
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -167,6 +178,9 @@ struct Args {
     const int* table;
     int n_requests, table_stride, page_tokens, n_heads, n_kv, window;
     float scale_log2;
+    float cap_log2, in_cap;    // capped scores: cap log2(e) and scale / cap (the kernel's CAPPED form)
+    const float* head_gate;    // null, or float32 [rows, gate_ld]: head h of row t is multiplied by sigmoid(head_gate[t, h])
+    int gate_ld;
     int plane_rows;            // rows of the [pages * n_kv * page_tokens, 128] view of a cache plane
     int block_rows;            // query rows a block takes: 256 (both tiles) or 128 (the second tile stays empty)
 };
@@ -178,6 +192,7 @@ struct QueryTile {
     int begin, end;    // key tiles [begin, end] it needs, counted from the block's first key tile (begin > end: none)
 };
 
+template <bool CAPPED>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Args p) {
@@ -446,8 +461,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
                     for (int c = 0; c < HC; c += 4) {
-                        const float2 t0 = unpack2(fma2(pack2(__uint_as_float(v[c]), __uint_as_float(v[c + 1])), scale2, sub2));
-                        const float2 t1 = unpack2(fma2(pack2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])), scale2, sub2));
+                        float2 t0, t1;
+                        if (CAPPED) {
+                            t0 = make_float2(capped_score(__uint_as_float(v[c]), p.in_cap, p.cap_log2, neg_sub),
+                                             capped_score(__uint_as_float(v[c + 1]), p.in_cap, p.cap_log2, neg_sub));
+                            t1 = make_float2(capped_score(__uint_as_float(v[c + 2]), p.in_cap, p.cap_log2, neg_sub),
+                                             capped_score(__uint_as_float(v[c + 3]), p.in_cap, p.cap_log2, neg_sub));
+                        } else {
+                            t0 = unpack2(fma2(pack2(__uint_as_float(v[c]), __uint_as_float(v[c + 1])), scale2, sub2));
+                            t1 = unpack2(fma2(pack2(__uint_as_float(v[c + 2]), __uint_as_float(v[c + 3])), scale2, sub2));
+                        }
                         const float e0 = ex2(t0.x), e1 = ex2(t0.y), e2 = ex2(t1.x), e3 = ex2(t1.y);
                         sum2a = add2(sum2a, pack2(e0, e1));
                         sum2b = add2(sum2b, pack2(e2, e3));
@@ -460,7 +483,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const float2 sa = unpack2(sum2a), sb = unpack2(sum2b);
                     sum = (sa.x + sa.y) + (sb.x + sb.y);
                     if (attempt == 1) break;
-                    const float mx = fmaxf(mx0, mx1) * p.scale_log2;                         // scale > 0
+                    // scale > 0, and capping keeps the order: the largest raw score is the largest score
+                    const float mx = CAPPED ? capped_score(fmaxf(mx0, mx1), p.in_cap, p.cap_log2, 0.0f) : fmaxf(mx0, mx1) * p.scale_log2;
                     float m_new = m_ref;
                     if (mx > m_ref + RESCALE_THRESHOLD || m_ref == -INFINITY) m_new = fmaxf(m_ref, mx);
                     if (!__any_sync(0xffffffffu, m_new != m_ref)) break;
@@ -501,7 +525,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && n_mine > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_done[g], 0, 18));
         if (ok && n_mine > 0) {
             tcgen05_fence_after();
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            if (p.head_gate && r < mine.rows) inv *= 1.0f / (1.0f + expf(-p.head_gate[(size_t)(row0 + g * BM + r) * p.gate_ld + h]));
             __nv_bfloat16* dst = p.out + ((size_t)(row0 + g * BM + r) * p.n_heads + h) * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 16) {
@@ -540,11 +565,13 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols
 
 // q, out: [T, n_heads, 128] bf16; planes [pages, n_kv, 16, 128] bf16; req_start [n_requests + 1],
 // req_prior [n_requests].  Head size 128 and 16-token pages only; refuses anything else.  force_block_rows: 128 or 256
-// query rows a block, or 0 to let the launch's size decide.
+// query rows a block, or 0 to let the launch's size decide.  softcap > 0: a score becomes cap tanh(s / cap)
+// after the scale.  head_gate: null, or float32 with row stride gate_ld whose entry [t, h] gates head h of row t.
 CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kplane, const void* vplane, int n_pages,
                                       const int* req_start, const int* req_prior, int n_requests, int total_rows,
                                       const int* table, int table_stride, int page_tokens, int n_heads, int n_kv,
-                                      int hd, int window, float scale, int force_block_rows, cudaStream_t stream) {
+                                      int hd, int window, float scale, int force_block_rows, float softcap,
+                                      const float* head_gate, int gate_ld, cudaStream_t stream) {
     if (total_rows <= 0 || n_requests <= 0) return 0;
     if (!q || !out || !kplane || !vplane || !req_start || !req_prior || !table) return CJ_ERR_ARG;
     if (hd != HD || page_tokens != 16) return CJ_ERR_SIZE;
@@ -558,7 +585,9 @@ CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kpla
     if (!make_map(&mv, vplane, plane_rows, HD, HD, 16)) return CJ_ERR_ARG;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(prefill_attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -578,13 +607,15 @@ CJ_EXPORT int cj_prefill_attention_tc(const void* q, void* out, const void* kpla
         block_rows = 2 * blocks_256 <= sm_count ? 128 : 256;
     }
     Args a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, req_start, req_prior, table, n_requests, table_stride, page_tokens,
-           n_heads, n_kv, window, scale * 1.4426950408889634f, (int)plane_rows, block_rows};
+           n_heads, n_kv, window, scale * 1.4426950408889634f, softcap * 1.4426950408889634f,
+           softcap > 0.0f ? scale / softcap : 0.0f, head_gate, gate_ld, (int)plane_rows, block_rows};
     // heads run fastest, so that blocks start in the order of their length (the last rows of a
     // request see the most keys) and the heads of one group read the same keys one after another
     const long long row_blocks = (total_rows + block_rows - 1) / block_rows + n_requests;
     if (row_blocks > 65535) return CJ_ERR_SIZE;
     dim3 grid(n_heads, (unsigned)row_blocks);
-    cj::launch(prefill_attention_tc_kernel, dim3(grid), dim3(THREADS), SMEM_TOTAL, stream, mq, mk, mv, a);
+    if (softcap > 0.0f) cj::launch(prefill_attention_tc_kernel<true>, dim3(grid), dim3(THREADS), SMEM_TOTAL, stream, mq, mk, mv, a);
+    else cj::launch(prefill_attention_tc_kernel<false>, dim3(grid), dim3(THREADS), SMEM_TOTAL, stream, mq, mk, mv, a);
     return cj::launch_status();
 }
 

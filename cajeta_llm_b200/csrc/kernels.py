@@ -246,6 +246,14 @@ def head_prepare(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: tor
     _check(st, "head_prepare")
 
 
+def _gate(head_gate: Optional[torch.Tensor], gate_offset: int):
+    """Pointer to column ``gate_offset`` of a float32 [T, ld] tensor of per-head gate values, and ld."""
+    if head_gate is None:
+        return ctypes.c_void_p(0), 0
+    _need(head_gate, "head_gate", torch.float32)
+    return ctypes.c_void_p(head_gate.data_ptr() + 4 * gate_offset), head_gate.stride(0)
+
+
 def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                     positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
                     n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, value_dim: int = 0,
@@ -258,10 +266,7 @@ def paged_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v
     T = q.shape[0]
     if head_dim > 256:
         raise KernelError(f"paged_attention: head_dim {head_dim} is larger than 256")
-    gate_ptr, gate_ld = ctypes.c_void_p(0), 0
-    if head_gate is not None:
-        _need(head_gate, "head_gate", torch.float32)
-        gate_ptr, gate_ld = ctypes.c_void_p(head_gate.data_ptr() + 4 * gate_offset), head_gate.stride(0)
+    gate_ptr, gate_ld = _gate(head_gate, gate_offset)
     st = library("attention_paged").cj_paged_attention(
         _ptr(q), _ptr(out), _i(_code(q)), _ptr(k_plane), _ptr(v_plane), _i(_code(k_plane)), _ptr(positions),
         _ptr(row_req), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim),
@@ -858,19 +863,22 @@ def decode_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, 
                      positions: torch.Tensor, row_req: torch.Tensor, table: torch.Tensor, page_tokens: int,
                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, max_context: int,
                      scratch: "DecodeScratch", chunk: int = 0, tensor_cores: Optional[bool] = None,
-                     merge_later: Optional[bool] = None) -> None:
+                     merge_later: Optional[bool] = None, softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None,
+                     gate_offset: int = 0) -> None:
     """Split-KV attention of few bfloat16 query rows over their cached keys (head_dim 64 or 128).
     ``tensor_cores``: scores and weighted values of a chunk by mma.sync (the default) or on the
     FMA pipe (``chunk`` 64 or 128 applies to that form only).  ``merge_later``: the chunks of a
     row are merged by a kernel of its own instead of the row's last block (the default for steps
-    with many rows; same results to the bit)."""
+    with many rows; same results to the bit).  ``softcap`` and ``head_gate`` as in ``paged_attention``
+    (tensor-core form only)."""
     for n, t in (("q", q), ("out", out), ("k_plane", k_plane), ("v_plane", v_plane)):
         _need(t, n, torch.bfloat16)
     _need(positions, "positions", torch.int32), _need(row_req, "row_req", torch.int32), _need(table, "table", torch.int32)
     T = q.shape[0]
     span = min(window, max_context) if window > 0 else max_context
+    gate_ptr, gate_ld = _gate(head_gate, gate_offset)
     if tensor_cores is None:
-        tensor_cores = DECODE_TENSOR_CORES and chunk == 0
+        tensor_cores = (DECODE_TENSOR_CORES and chunk == 0) or softcap > 0.0 or head_gate is not None
     if tensor_cores:
         splits = max(1, -(-span // 128))
         scratch.ensure(T, n_heads, n_kv, head_dim, splits, q.device)
@@ -880,12 +888,14 @@ def decode_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, 
             _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(positions), _ptr(row_req), _ptr(table),
             _i(table.stride(0)), _i(page_tokens), _i(T), _i(n_heads), _i(n_kv), _i(head_dim), _i(window), _f(scale),
             _i(max_context), _ptr(scratch.acc), _ptr(scratch.ml), _ptr(scratch.counters), _i(scratch.splits),
-            _i(1 if merge_later else 0), _stream())
+            _i(1 if merge_later else 0), _f(softcap), gate_ptr, _i(gate_ld), _stream())
         _check(st, "decode_attention")
         if merge_later and splits > 1:
             global launches
             launches += 1                  # the merge kernel
         return
+    if softcap > 0.0 or head_gate is not None:
+        raise KernelError("decode_attention: capped scores and gated heads are built into the tensor-core form only")
     chunk = chunk or decode_chunk(span)
     splits = max(1, -(-span // chunk))
     scratch.ensure(T, n_heads, n_kv, head_dim, splits, q.device)
@@ -916,22 +926,26 @@ class DecodeScratch:
 
 def prefill_attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                       req_start: torch.Tensor, req_prior: torch.Tensor, table: torch.Tensor, page_tokens: int,
-                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, block_rows: int = 0) -> None:
+                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, block_rows: int = 0,
+                      softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
     """Tensor-core attention of a step's rows (request r owns rows req_start[r]..req_start[r+1]
-    at positions req_prior[r] + i) over the paged cache; bfloat16, head_dim 64 or 128."""
+    at positions req_prior[r] + i) over the paged cache; bfloat16, head_dim 32, 64, 96 or 128.
+    ``softcap`` and ``head_gate`` as in ``paged_attention``."""
     for n, t in (("q", q), ("out", out), ("k_plane", k_plane), ("v_plane", v_plane)):
         _need(t, n, torch.bfloat16)
     _need(req_start, "req_start", torch.int32), _need(req_prior, "req_prior", torch.int32), _need(table, "table", torch.int32)
+    gate_ptr, gate_ld = _gate(head_gate, gate_offset)
     st = library("attention_prefill").cj_prefill_attention(
         _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _ptr(req_start), _ptr(req_prior), _i(req_prior.numel()),
         _i(q.shape[0]), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv), _i(head_dim), _i(window),
-        _f(scale), _i(block_rows), _stream())
+        _f(scale), _i(block_rows), _f(softcap), gate_ptr, _i(gate_ld), _stream())
     _check(st, "prefill_attention")
 
 
 def prefill_attention_tc(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
                          req_start: torch.Tensor, req_prior: torch.Tensor, table: torch.Tensor, page_tokens: int,
-                         n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, block_rows: int = 0) -> None:
+                         n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, block_rows: int = 0,
+                         softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
     """The same contract as ``prefill_attention`` on the tcgen05 tensor cores: both products
     from shared memory into tensor memory.  ``block_rows``: 256 query rows a block (two tiles
     taking turns), 128, or 0 = by the size of the launch.  Head size 128 and pages of 16 tokens
@@ -941,10 +955,11 @@ def prefill_attention_tc(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tens
     _need(req_start, "req_start", torch.int32), _need(req_prior, "req_prior", torch.int32), _need(table, "table", torch.int32)
     if head_dim != 128 or page_tokens != 16:
         raise KernelError(f"prefill_attention_tc takes head size 128 and 16-token pages, not {head_dim} and {page_tokens}")
+    gate_ptr, gate_ld = _gate(head_gate, gate_offset)
     st = library("attention_prefill_tc").cj_prefill_attention_tc(
         _ptr(q), _ptr(out), _ptr(k_plane), _ptr(v_plane), _i(k_plane.shape[0]), _ptr(req_start), _ptr(req_prior),
         _i(req_prior.numel()), _i(q.shape[0]), _ptr(table), _i(table.stride(0)), _i(page_tokens), _i(n_heads), _i(n_kv),
-        _i(head_dim), _i(window), _f(scale), _i(block_rows), _stream())
+        _i(head_dim), _i(window), _f(scale), _i(block_rows), _f(softcap), gate_ptr, _i(gate_ld), _stream())
     _check(st, "prefill_attention_tc")
 
 

@@ -119,6 +119,11 @@ class PagedAttention(Part):
         libs = {"rowwise", "gemm_simt"}
         if self.general:
             libs.add("attention_paged")
+            if self.runtime.fast_kernels and self.value_dim == self.head_dim:
+                if self.head_dim in (64, 128):
+                    libs.add("attention_decode")
+                if self.head_dim in (32, 64, 96, 128):
+                    libs.add("attention_prefill_tc" if self.head_dim == 128 else "attention_prefill")
         elif self.runtime.fast_kernels and self.head_dim in (64, 128):
             libs |= {"attention_decode", "attention_prefill_tc" if self.head_dim == 128 else "attention_prefill"}
         else:
@@ -210,9 +215,28 @@ class PagedAttention(Part):
                        float(self.qk_norm["eps"]) if self.qk_norm else 0.0, write)
         out = torch.empty((T, self.heads, self.value_dim), dtype=rt.act_dtype, device=x.device)
         K.tag = "attention"
-        K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens,
-                          self.heads, self.kv_heads, self.head_dim, self.window, self.scale, value_dim=self.value_dim,
-                          softcap=self.softcap, head_gate=qkv if gate_cols else None, gate_offset=g_off)
+        gate = qkv if gate_cols else None
+        fast = rt.fast_kernels and self.value_dim == self.head_dim
+        if fast and getattr(ctx, "all_single", False) and self.head_dim in (64, 128):
+            # every request brings one token: the split-KV decode kernel
+            K.decode_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table,
+                               entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale,
+                               ctx.max_context, getattr(ctx, "decode_scratch", None) or rt.decode_scratch,
+                               softcap=self.softcap, head_gate=gate, gate_offset=g_off)
+        elif fast and self.head_dim == 128 and entry.page_tokens == 16 and hasattr(ctx, "req_start"):
+            # portions of prompts (and whatever single tokens ride along): both products on tcgen05
+            K.prefill_attention_tc(q, out, entry.k_plane, entry.v_plane, ctx.req_start, ctx.req_prior, entry.block_table,
+                                   entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale,
+                                   softcap=self.softcap, head_gate=gate, gate_offset=g_off)
+        elif fast and self.head_dim in (32, 64, 96, 128) and hasattr(ctx, "req_start"):
+            # portions of prompts (and whatever single tokens ride along): query tiles on the tensor cores
+            K.prefill_attention(q, out, entry.k_plane, entry.v_plane, ctx.req_start, ctx.req_prior, entry.block_table,
+                                entry.page_tokens, self.heads, self.kv_heads, self.head_dim, self.window, self.scale,
+                                softcap=self.softcap, head_gate=gate, gate_offset=g_off)
+        else:
+            K.paged_attention(q, out, entry.k_plane, entry.v_plane, ctx.positions, ctx.row_req, entry.block_table, entry.page_tokens,
+                              self.heads, self.kv_heads, self.head_dim, self.window, self.scale, value_dim=self.value_dim,
+                              softcap=self.softcap, head_gate=gate, gate_offset=g_off)
         K.tag = "o"
         parts = project_split(rt, out.view(T, self.o_dim), self.w_o) if self.allow_pending else None
         if parts is None:
