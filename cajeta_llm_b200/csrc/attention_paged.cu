@@ -155,6 +155,20 @@ CJ_EXPORT int cj_paged_attention(const void* q, void* out, int act_dtype, const 
 // place in the paged cache.  v_off < 0: the values are the keys as projected, before norm
 // and rotation (vd == hd then).  All arithmetic is float32.
 // ---------------------------------------------------------------------------------
+__device__ __forceinline__ void store4(float* dst, float4 v) { *(float4*)dst = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *(unsigned*)&lo;
+    u.y = *(unsigned*)&hi;
+    *(uint2*)dst = u;
+}
+__device__ __forceinline__ float4 mul4(float4 a, float f) { return make_float4(a.x * f, a.y * f, a.z * f, a.w * f); }
+__device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+
+// One block per row (with few rows the row's heads are shared out over gridDim.y blocks): the row's cos
+// and sin are worked out once into shared memory, then a warp takes a head at a time.  Head sizes, rotary
+// parts and offsets that are multiples of four go four entries a lane (16-byte loads, 8- or 16-byte stores).
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(128) head_prepare_kernel(
     const float* __restrict__ x, int ld, int q_off, int k_off, int v_off, TQ* __restrict__ q_out, TC* __restrict__ kplane,
@@ -163,48 +177,87 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(
     float magnitude, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, int write_kv) {
     cj::after_predecessor();
     cj::release_successor();
-    const int lane = threadIdx.x & 31;
-    const int slots = n_heads + (write_kv ? n_kv : 0);
-    const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (unit >= (long long)T * slots) return;
-    const int t = (int)(unit / slots), slot = (int)(unit % slots);
-    const bool is_q = slot < n_heads;
-    const int head = is_q ? slot : slot - n_heads;
-    const float* src = x + (size_t)t * ld + (is_q ? q_off : k_off) + head * hd;
-    const float* nw = is_q ? q_norm : k_norm;
+    extern __shared__ __align__(16) float cs[];      // cos[half] then sin[half], times the magnitude
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x;
     const int pos = positions[t];
-    float inv = 1.0f;
-    if (nw) {
-        float ss = 0.0f;
-        for (int d = lane; d < hd; d += 32) ss = fmaf(src[d], src[d], ss);
-        ss = warp_sum(ss);
-        inv = 1.0f / sqrtf(ss / (float)hd + eps);
-    }
-    size_t place = 0;
-    bool have_page = false;
-    if (!is_q) {
-        int page = table[(size_t)row_req[t] * table_stride + pos / page_tokens];
-        have_page = page >= 0;                       // no page: the host never schedules this
-        place = ((size_t)(have_page ? page : 0) * n_kv + head) * page_tokens + pos % page_tokens;
-        if (!have_page) return;
-    }
     const int half = rot >> 1;
-    for (int d = lane; d < hd; d += 32) {
-        float a = src[d] * inv * (nw ? nw[d] : 1.0f);
-        float r = a;
-        if (d < rot) {
-            const int i = d < half ? d : d - half, pd = d < half ? d + half : d - half;
-            const float b = src[pd] * inv * (nw ? nw[pd] : 1.0f);
-            const float ang = (float)pos * inv_freq[i];
-            const float c = cosf(ang) * magnitude, s = sinf(ang) * magnitude;
-            r = d < half ? a * c - b * s : a * c + b * s;
-        }
-        if (is_q) q_out[((size_t)t * n_heads + head) * hd + d] = from_f32<TQ>(r);
-        else kplane[place * hd + d] = from_f32<TC>(r);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * inv_freq[i];
+        cs[i] = cosf(ang) * magnitude;
+        cs[half + i] = sinf(ang) * magnitude;
     }
-    if (!is_q) {
-        const float* vs = v_off < 0 ? src : x + (size_t)t * ld + v_off + head * vd;
-        for (int d = lane; d < vd; d += 32) vplane[place * vd + d] = from_f32<TC>(vs[d]);
+    size_t place0 = 0;
+    bool have_page = false;
+    if (write_kv) {
+        const int page = table[(size_t)row_req[t] * table_stride + pos / page_tokens];
+        have_page = page >= 0;                       // no page: the host never schedules this
+        place0 = (size_t)(have_page ? page : 0) * n_kv * page_tokens + pos % page_tokens;
+    }
+    __syncthreads();
+    const int slots = n_heads + (write_kv && have_page ? n_kv : 0);
+    const float* xrow = x + (size_t)t * ld;
+    const bool vec = (hd % 4 == 0) && (half % 4 == 0) && (vd % 4 == 0) && ((ld | q_off | k_off | (v_off < 0 ? 0 : v_off)) % 4 == 0) &&
+                     ((((uintptr_t)x) | ((uintptr_t)q_out) | ((uintptr_t)kplane) | ((uintptr_t)vplane) | ((uintptr_t)q_norm) |
+                       ((uintptr_t)k_norm)) & 15) == 0;
+    for (int slot = blockIdx.y * 4 + warp; slot < slots; slot += gridDim.y * 4) {
+        const bool is_q = slot < n_heads;
+        const int head = is_q ? slot : slot - n_heads;
+        const float* src = xrow + (is_q ? q_off : k_off) + head * hd;
+        const float* nw = is_q ? q_norm : k_norm;
+        const size_t place = place0 + (size_t)head * page_tokens;
+        float inv = 1.0f;
+        if (nw) {
+            float ss = 0.0f;
+            if (vec) {
+                for (int d = lane * 4; d < hd; d += 128) {
+                    const float4 a = *(const float4*)(src + d);
+                    ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss))));
+                }
+            } else {
+                for (int d = lane; d < hd; d += 32) ss = fmaf(src[d], src[d], ss);
+            }
+            ss = warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)hd + eps);
+        }
+        if (vec) {
+            for (int d = lane * 4; d < hd; d += 128) {
+                float4 a = mul4(*(const float4*)(src + d), inv);
+                if (nw) a = mul4(a, *(const float4*)(nw + d));
+                if (d < rot) {
+                    const bool low = d < half;
+                    const int i = low ? d : d - half, pd = low ? d + half : d - half;
+                    float4 b = mul4(*(const float4*)(src + pd), inv);
+                    if (nw) b = mul4(b, *(const float4*)(nw + pd));
+                    const float4 c = *(const float4*)(cs + i), sn = *(const float4*)(cs + half + i);
+                    const float sg = low ? -1.0f : 1.0f;
+                    a = make_float4(fmaf(sg * b.x, sn.x, a.x * c.x), fmaf(sg * b.y, sn.y, a.y * c.y), fmaf(sg * b.z, sn.z, a.z * c.z),
+                                    fmaf(sg * b.w, sn.w, a.w * c.w));
+                }
+                if (is_q) store4(q_out + ((size_t)t * n_heads + head) * hd + d, a);
+                else store4(kplane + place * hd + d, a);
+            }
+            if (!is_q) {
+                const float* vs = v_off < 0 ? src : xrow + v_off + head * vd;
+                for (int d = lane * 4; d < vd; d += 128) store4(vplane + place * vd + d, *(const float4*)(vs + d));
+            }
+            continue;
+        }
+        for (int d = lane; d < hd; d += 32) {
+            float a = src[d] * inv * (nw ? nw[d] : 1.0f);
+            float r = a;
+            if (d < rot) {
+                const int i = d < half ? d : d - half, pd = d < half ? d + half : d - half;
+                const float b = src[pd] * inv * (nw ? nw[pd] : 1.0f);
+                r = d < half ? a * cs[i] - b * cs[half + i] : a * cs[i] + b * cs[half + i];
+            }
+            if (is_q) q_out[((size_t)t * n_heads + head) * hd + d] = from_f32<TQ>(r);
+            else kplane[place * hd + d] = from_f32<TC>(r);
+        }
+        if (!is_q) {
+            const float* vs = v_off < 0 ? src : xrow + v_off + head * vd;
+            for (int d = lane; d < vd; d += 32) vplane[place * vd + d] = from_f32<TC>(vs[d]);
+        }
     }
 }
 
@@ -219,10 +272,14 @@ CJ_EXPORT int cj_head_prepare(const float* x, int ld, int q_off, int k_off, int 
     if (rotary_dim > 0 && !inv_freq) return CJ_ERR_ARG;
     if (write_kv && (!kplane || !vplane || !row_req || !table || page_tokens <= 0 || n_kv <= 0)) return CJ_ERR_ARG;
     if (v_off < 0 && vd != hd) return CJ_ERR_SIZE;
-    const long long units = (long long)T * (n_heads + (write_kv ? n_kv : 0));
-    dim3 grid((unsigned)((units + 3) / 4));
+    // a warp a head; with few rows the heads of a row go over several blocks
+    const int slots = n_heads + (write_kv ? n_kv : 0);
+    int parts = T >= 128 ? 1 : (slots + 3) / 4;
+    if (parts > 16) parts = 16;
+    dim3 grid(T, parts);
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
 #define LAUNCH(TQ, TC)                                                                                                  \
-    cj::launch(head_prepare_kernel<TQ, TC>, dim3(grid), dim3(128), 0, stream, x, ld, q_off, k_off, v_off, (TQ*)q_out,  \
+    cj::launch(head_prepare_kernel<TQ, TC>, dim3(grid), dim3(128), smem, stream, x, ld, q_off, k_off, v_off, (TQ*)q_out,  \
         (TC*)kplane, (TC*)vplane, positions, row_req, table, table_stride, page_tokens, T, n_heads, n_kv, hd, vd,      \
         rotary_dim, inv_freq, magnitude, q_norm, k_norm, eps, write_kv)
     if (q_dtype == CJ_F32 && cache_dtype == CJ_F32) LAUNCH(float, float);

@@ -136,14 +136,16 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-// cap log2(e) tanh(x) - sub for a raw score s with x = s scale / cap; tanh(x) = 1 - 2 / (e^2x + 1) from
-// the fast exponential and reciprocal (absolute error of a few 2^-23: a capped score is exact to the
-// grade of the uncapped form's single rounding); a masked score (-inf) stays -inf
+// cap log2(e) tanh(x) - sub for a raw score s with x = s scale / cap; a masked score (-inf) stays -inf.
+// The softmax pass is bound by the special-function unit and by instruction issue, so the hyperbolic
+// tangent is the unit's own (tanh.approx.f32, relative error 2^-11: a capped score is off by at most that
+// share of itself, the size of the rounding its bfloat16 inputs already carry); measured on 2,048 x 2,048
+// scores of 16 heads: 38 us uncapped, 80 us with 1 - 2 / (e^2x + 1) from ex2 + rcp, 98 us with the
+// reciprocal by Newton steps on the FMA pipe instead.
 __device__ __forceinline__ float capped_score(float s, float in_cap, float cap_log2, float neg_sub) {
-    float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(s * in_cap * 2.8853900817779268f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
-    const float y = fmaf(fmaf(-2.0f, r, 1.0f), cap_log2, neg_sub);
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(s * in_cap));
+    const float y = fmaf(th, cap_log2, neg_sub);
     return s == -INFINITY ? -INFINITY : y;
 }
 

@@ -439,6 +439,26 @@ def gelu_gate(a: torch.Tensor, table: torch.Tensor, offset: int, ids: torch.Tens
     _check(st, "gelu_gate")
 
 
+SIDE_ROWS_MAX = 48        # steps with at most this many rows run the side input as one kernel, a block a row
+
+
+def side_rows(hs: torch.Tensor, w_gate: torch.Tensor, w_proj: torch.Tensor, norm_w: torch.Tensor, table: torch.Tensor,
+              offset: int, ids: torch.Tensor, eps: float) -> None:
+    """hs[t] += rms(W_proj (gelu_tanh(W_gate hs[t]) * table[ids[t], offset:offset + dim])) * norm_w in one kernel,
+    for few rows.  hs float32 [T, H] (H <= 8192); the weights and the table in one dtype; the row and the gated
+    vector are rounded to that dtype before their products, as the path of separate kernels does."""
+    _need(hs, "hs", torch.float32), _need(w_gate, "w_gate"), _need(w_proj, "w_proj", w_gate.dtype), _need(table, "table", w_gate.dtype)
+    _need(norm_w, "norm_w", torch.float32), _need(ids, "ids", torch.int32)
+    T, H = hs.shape
+    dim = w_gate.shape[0]
+    if w_gate.shape != (dim, H) or w_proj.shape != (H, dim) or norm_w.numel() != H or table.shape[1] < offset + dim:
+        raise KernelError("side_rows: sizes do not agree")
+    st = library("stream_ops").cj_side_rows(_ptr(hs), _ptr(w_gate), _ptr(w_proj), _ptr(norm_w), _ptr(table), _i(_code(w_gate)),
+                                            _i(table.stride(0)), _i(offset), _ptr(ids), _i(table.shape[0]), _i(T), _i(H), _i(dim),
+                                            _f(eps), _stream())
+    _check(st, "side_rows")
+
+
 def stream_cast(x: torch.Tensor, out: torch.Tensor) -> None:
     """out = x (float32) in out's dtype."""
     _need(x, "x", torch.float32), _need(out, "out")
