@@ -428,6 +428,16 @@ def add_rows(hs: torch.Tensor, other: Optional[torch.Tensor], vec: Optional[torc
     _check(library("stream_ops").cj_add_rows(_ptr(hs), _ptr(other), _ptr(vec), _i(T), _i(H), _stream()), "add_rows")
 
 
+def add_partials(hs: torch.Tensor, parts: torch.Tensor) -> None:
+    """hs += parts[0] + parts[1] + ... in that order; hs float32 [T, H], parts float32 [S, T, H] (the partial sums a
+    product cut along K leaves behind, when no norm follows that could add them while it reads the row)."""
+    _need(hs, "hs", torch.float32), _need(parts, "parts", torch.float32)
+    if parts.dim() != 3 or tuple(parts.shape[1:]) != tuple(hs.shape):
+        raise KernelError(f"add_partials: parts {tuple(parts.shape)} do not fit hs {tuple(hs.shape)}")
+    st = library("stream_ops").cj_add_partials(_ptr(hs), _ptr(parts), _i(parts.shape[0]), _ll(parts.stride(0)), _ll(hs.numel()), _stream())
+    _check(st, "add_partials")
+
+
 def gelu_gate(a: torch.Tensor, table: torch.Tensor, offset: int, ids: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, j] = gelu_tanh(a[t, j]) * table[ids[t], offset + j]; a float32 [T, >= n], out [T, n] in the table's dtype."""
     _need(a, "a", torch.float32), _need(table, "table"), _need(ids, "ids", torch.int32), _need(out, "out", table.dtype)
@@ -437,26 +447,6 @@ def gelu_gate(a: torch.Tensor, table: torch.Tensor, offset: int, ids: torch.Tens
     st = library("stream_ops").cj_gelu_gate(_ptr(a), _i(a.stride(0)), _ptr(table), _i(_code(table)), _i(table.stride(0)), _i(offset),
                                             _ptr(ids), _i(table.shape[0]), _ptr(out), _i(_code(out)), _i(T), _i(n), _stream())
     _check(st, "gelu_gate")
-
-
-SIDE_ROWS_MAX = 48        # steps with at most this many rows run the side input as one kernel, a block a row
-
-
-def side_rows(hs: torch.Tensor, w_gate: torch.Tensor, w_proj: torch.Tensor, norm_w: torch.Tensor, table: torch.Tensor,
-              offset: int, ids: torch.Tensor, eps: float) -> None:
-    """hs[t] += rms(W_proj (gelu_tanh(W_gate hs[t]) * table[ids[t], offset:offset + dim])) * norm_w in one kernel,
-    for few rows.  hs float32 [T, H] (H <= 8192); the weights and the table in one dtype; the row and the gated
-    vector are rounded to that dtype before their products, as the path of separate kernels does."""
-    _need(hs, "hs", torch.float32), _need(w_gate, "w_gate"), _need(w_proj, "w_proj", w_gate.dtype), _need(table, "table", w_gate.dtype)
-    _need(norm_w, "norm_w", torch.float32), _need(ids, "ids", torch.int32)
-    T, H = hs.shape
-    dim = w_gate.shape[0]
-    if w_gate.shape != (dim, H) or w_proj.shape != (H, dim) or norm_w.numel() != H or table.shape[1] < offset + dim:
-        raise KernelError("side_rows: sizes do not agree")
-    st = library("stream_ops").cj_side_rows(_ptr(hs), _ptr(w_gate), _ptr(w_proj), _ptr(norm_w), _ptr(table), _i(_code(w_gate)),
-                                            _i(table.stride(0)), _i(offset), _ptr(ids), _i(table.shape[0]), _i(T), _i(H), _i(dim),
-                                            _f(eps), _stream())
-    _check(st, "side_rows")
 
 
 def stream_cast(x: torch.Tensor, out: torch.Tensor) -> None:

@@ -65,6 +65,28 @@ __global__ void add_rows_kernel(float* __restrict__ hs, const float* __restrict_
     }
 }
 
+// hs[i] += parts[0][i] + parts[1][i] + ... in that order (partial sums of a product cut along K)
+template <bool VEC>
+__global__ void add_partials_kernel(float* __restrict__ hs, const float* __restrict__ parts, int n_parts, long long stride, long long n) {
+    cj::after_predecessor();
+    cj::release_successor();
+    constexpr int W = VEC ? 4 : 1;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * W; i < n; i += (long long)gridDim.x * blockDim.x * W) {
+        if (VEC) {
+            float4 v = *(const float4*)(hs + i);
+            for (int s = 0; s < n_parts; ++s) {
+                const float4 p = *(const float4*)(parts + s * stride + i);
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+            *(float4*)(hs + i) = v;
+        } else {
+            float v = hs[i];
+            for (int s = 0; s < n_parts; ++s) v += parts[s * stride + i];
+            hs[i] = v;
+        }
+    }
+}
+
 __device__ __forceinline__ float gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -110,84 +132,7 @@ __global__ void __launch_bounds__(256) norm_add_kernel(float* __restrict__ hs, c
     for (int i = threadIdx.x; i < H; i += blockDim.x) hs[base + i] += y[base + i] * inv * w[i];
 }
 
-// The whole side input for steps with few rows, one block a row: the row of the stream (rounded to the
-// weights' type, as the product of the many-row path reads it), a = W_gate x by a warp per output,
-// g = gelu_tanh(a) * table[token, offset + j] (rounded likewise), y = W_proj g by a thread per output,
-// hs += y / sqrt(mean y^2 + eps) * w.  Sums in float32, each in a fixed order.
-template <typename TW>
-__global__ void __launch_bounds__(256) side_rows_kernel(float* __restrict__ hs, const TW* __restrict__ w_gate,
-                                                        const TW* __restrict__ w_proj, const float* __restrict__ norm_w,
-                                                        const TW* __restrict__ table, int ldt, int offset,
-                                                        const int* __restrict__ ids, int V, int H, int dim, float eps) {
-    cj::after_predecessor();
-    cj::release_successor();
-    extern __shared__ float sm[];
-    float* xs = sm;              // [H] the row, rounded
-    float* gs = sm + H;          // [dim]
-    __shared__ float part[8];
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float* row = hs + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += 256) xs[i] = to_f32(from_f32<TW>(row[i]));
-    __syncthreads();
-    const int id = ids[t];
-    const bool ok = id >= 0 && id < V;
-    const TW* e = table + (size_t)(ok ? id : 0) * ldt + offset;
-    for (int j = warp; j < dim; j += 8) {
-        const TW* wr = w_gate + (size_t)j * H;
-        float a = 0.0f;
-        for (int i = lane; i < H; i += 32) a = fmaf(to_f32(wr[i]), xs[i], a);
-        a = warp_sum(a);
-        if (lane == 0) gs[j] = ok ? to_f32(from_f32<TW>(gelu_tanh(a) * to_f32(e[j]))) : 0.0f;
-    }
-    __syncthreads();
-    // y stays in registers: a thread owns outputs threadIdx.x, threadIdx.x + 256, ... (at most 32 of them)
-    float y[32];
-    float ss = 0.0f;
-#pragma unroll
-    for (int k = 0; k < 32; ++k) {
-        const int i = threadIdx.x + k * 256;
-        y[k] = 0.0f;
-        if (i < H) {
-            const TW* wr = w_proj + (size_t)i * dim;
-            float acc = 0.0f;
-            for (int j = 0; j < dim; ++j) acc = fmaf(to_f32(wr[j]), gs[j], acc);
-            y[k] = acc;
-            ss = fmaf(acc, acc, ss);
-        }
-    }
-    ss = warp_sum(ss);
-    if (lane == 0) part[warp] = ss;
-    __syncthreads();
-    float total = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) total += part[i];
-    const float inv = 1.0f / sqrtf(total / (float)H + eps);
-#pragma unroll
-    for (int k = 0; k < 32; ++k) {
-        const int i = threadIdx.x + k * 256;
-        if (i < H) row[i] += y[k] * inv * norm_w[i];
-    }
-}
-
 }  // namespace
-
-// hs float32 [T, H]; w_gate [dim, H], w_proj [H, dim] and table [V, ldt] in one type (float32 or bfloat16).  H <= 8192.
-CJ_EXPORT int cj_side_rows(float* hs, const void* w_gate, const void* w_proj, const float* norm_w, const void* table,
-                           int w_dtype, int ldt, int offset, const int* ids, int V, int T, int H, int dim, float eps,
-                           cudaStream_t stream) {
-    if (T <= 0) return 0;
-    if (!hs || !w_gate || !w_proj || !norm_w || !table || !ids) return CJ_ERR_ARG;
-    if (H <= 0 || H > 8192 || dim <= 0 || dim > 2048) return CJ_ERR_SIZE;      // the row and the gated vector fit 40 KB of shared memory
-    const size_t smem = (size_t)(H + dim) * sizeof(float);
-    if (w_dtype == CJ_BF16)
-        cj::launch(side_rows_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, hs, (const __nv_bfloat16*)w_gate,
-                   (const __nv_bfloat16*)w_proj, norm_w, (const __nv_bfloat16*)table, ldt, offset, ids, V, H, dim, eps);
-    else if (w_dtype == CJ_F32)
-        cj::launch(side_rows_kernel<float>, dim3(T), dim3(256), smem, stream, hs, (const float*)w_gate, (const float*)w_proj,
-                   norm_w, (const float*)table, ldt, offset, ids, V, H, dim, eps);
-    else return CJ_ERR_DTYPE;
-    return launch_status();
-}
 
 CJ_EXPORT int cj_stream_cast(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
     if (n <= 0) return 0;
@@ -238,6 +183,17 @@ CJ_EXPORT int cj_add_rows(float* hs, const float* other, const float* vec, int T
     if (T <= 0 || (!other && !vec)) return 0;
     if (!hs || H <= 0) return CJ_ERR_ARG;
     cj::launch(add_rows_kernel, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream, hs, other, vec, H);
+    return launch_status();
+}
+
+CJ_EXPORT int cj_add_partials(float* hs, const float* parts, int n_parts, long long stride, long long n, cudaStream_t stream) {
+    if (n <= 0 || n_parts <= 0) return 0;
+    if (!hs || !parts) return CJ_ERR_ARG;
+    const bool vec = (n | stride) % 4 == 0 && ((((uintptr_t)hs) | ((uintptr_t)parts)) & 15) == 0;
+    long long blocks = (n / (vec ? 4 : 1) + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (vec) cj::launch(add_partials_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, stream, hs, parts, n_parts, stride, n);
+    else cj::launch(add_partials_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, stream, hs, parts, n_parts, stride, n);
     return launch_status();
 }
 

@@ -139,8 +139,6 @@ class ParallelBlock(Part):
         super().__init__(spec, prefix, runtime)
         self.mixer_norm = make_part("norm", layer.mixer_norm, self.name(spec["mixer_norm_name"]), runtime)
         self.mixer = make_part("mixer", layer.mixer, self.name(spec["mixer_name"]), runtime)
-        # no norm follows the mixer inside this block: it adds its whole result itself
-        self.mixer.allow_pending = False
         self.feed_forward = None
         if layer.feed_forward is not None:
             self.feed_forward = make_part("feed_forward", layer.feed_forward, self.name(spec["feed_forward_name"]), runtime)
@@ -158,7 +156,7 @@ class ParallelBlock(Part):
         return out
 
     def libraries(self) -> set:
-        out = set()
+        out = {"stream_ops"}
         for p in self.parts():
             out |= p.libraries()
         return out
@@ -172,9 +170,13 @@ class ParallelBlock(Part):
         wants_split = getattr(ff, "wants_split_input", None)
         split = bool(wants_split and wants_split(hs.shape[0]))
         x, x_exact = self.mixer_norm.forward(hs, want_f32=getattr(ff, "needs_f32_input", False) and not split, want_split=split)
+        # partial sums a mixer still owes the stream (its output product cut along K for few rows): no norm
+        # follows inside this block that could add them while it reads the row, so a kernel of its own does
         pending = self.mixer.forward(x, hs, ctx, entry)
         if pending is not None:
-            raise RuntimeError("a parallel block's mixer must add its result itself (it returned partial sums)")
+            K.tag = "o (partial sums)"
+            K.add_partials(hs, pending)
+            K.tag = None
         if ff is not None:
             ff.forward(x, x_exact, hs, ctx)
         if self.after is not None:

@@ -14,8 +14,7 @@ the step function keeps in ``ctx.embedding_output`` for a plan that asks for it)
 ``[offset, offset + dim)`` of row ``token`` of a table shared by the layers:
 ``g = gelu_tanh(W_gate hs) * e``; ``y = W_proj g``; ``hs += y / sqrt(mean(y^2) + eps) * w``.  The
 norm's statistics and the add are float32; the two products read the stream and ``g`` in the
-activation dtype.  Steps with few rows run all of it as one kernel (a block a row), steps with many rows
-as a cast, two products and two row-wise kernels.  Parameters: ``hidden_size``, ``dim``, ``offset``, ``table_name`` (from the
+activation dtype.  Parameters: ``hidden_size``, ``dim``, ``offset``, ``table_name`` (from the
 model's root) and ``table_shape``, ``eps``, ``names`` (``gate``, ``proj``, ``norm`` under the part's
 prefix).
 """
@@ -104,12 +103,6 @@ class TokenSide(Part):
     def forward(self, hs: torch.Tensor, ctx) -> None:
         rt = self.runtime
         T = hs.shape[0]
-        if T <= K.SIDE_ROWS_MAX and self.hidden <= 8192 and self.dim <= 2048:
-            # few rows: the five steps below as one kernel, a block a row
-            K.tag = "side (one kernel)"
-            K.side_rows(hs, self.w_gate, self.w_proj, self.norm_w, self.table, self.offset, ctx.token_ids, self.eps)
-            K.tag = None
-            return
         x = hs
         if rt.act_dtype != torch.float32:
             x = torch.empty(hs.shape, dtype=rt.act_dtype, device=hs.device)
