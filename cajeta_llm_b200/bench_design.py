@@ -54,7 +54,7 @@ def saropel_config(s):
            "shared": {"ff": s["eff"], "limit": 7.0}}
     dense = {"kind": "dense", "ff": s["ff"]}
     return {"architecture": "Saropel", "width": h, "vocab": VOCAB, "norm": {"eps": 1e-6},
-            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 7}}, "token_side": {"dim": 256},
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 37, "mul_cur": 11}}, "token_side": {"dim": 256},
             "loop": {"start": 1, "stop": 2, "times": 2},
             "layers": [{"type": "attention", "mixer": capped, "mlp": dense}, {"type": "attention_2", "mixer": rotated, "mlp": moe},
                        {"type": "attention", "mixer": capped, "mlp": dense}]}

@@ -956,7 +956,7 @@ def prefill_attention_tc(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tens
                          req_start: torch.Tensor, req_prior: torch.Tensor, table: torch.Tensor, page_tokens: int,
                          n_heads: int, n_kv: int, head_dim: int, window: int, scale: float, block_rows: int = 0,
                          softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> None:
-    """The same contract as ``prefill_attention`` on the tcgen05 tensor cores: both products
+    """The same arguments and meaning as ``prefill_attention``, on the tcgen05 tensor cores: both products
     from shared memory into tensor memory.  ``block_rows``: 256 query rows a block (two tiles
     taking turns), 128, or 0 = by the size of the launch.  Head size 128 and pages of 16 tokens
     only; anything else is refused."""
