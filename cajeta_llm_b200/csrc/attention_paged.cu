@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(
     __syncthreads();
     const int slots = n_heads + (write_kv && have_page ? n_kv : 0);
     const float* xrow = x + (size_t)t * ld;
-    const bool vec = (hd % 4 == 0) && (half % 4 == 0) && (vd % 4 == 0) && ((ld | q_off | k_off | (v_off < 0 ? 0 : v_off)) % 4 == 0) &&
+    const bool vec = (hd % 4 == 0) && hd <= 256 && (half % 4 == 0) && (vd % 4 == 0) && ((ld | q_off | k_off | (v_off < 0 ? 0 : v_off)) % 4 == 0) &&
                      ((((uintptr_t)x) | ((uintptr_t)q_out) | ((uintptr_t)kplane) | ((uintptr_t)vplane) | ((uintptr_t)q_norm) |
                        ((uintptr_t)k_norm)) & 15) == 0;
     for (int slot = blockIdx.y * 4 + warp; slot < slots; slot += gridDim.y * 4) {
@@ -207,11 +207,22 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(
         const float* nw = is_q ? q_norm : k_norm;
         const size_t place = place0 + (size_t)head * page_tokens;
         float inv = 1.0f;
+        // the four-a-lane form keeps the head's entries (at most 256: two groups of four a lane) in registers
+        // between the sum of squares and the rotation
+        float4 held[2];
+        if (vec) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int d = lane * 4 + k * 128;
+                held[k] = d < hd ? *(const float4*)(src + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        }
         if (nw) {
             float ss = 0.0f;
             if (vec) {
-                for (int d = lane * 4; d < hd; d += 128) {
-                    const float4 a = *(const float4*)(src + d);
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const float4 a = held[k];
                     ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, fmaf(a.w, a.w, ss))));
                 }
             } else {
@@ -221,8 +232,11 @@ __global__ void __launch_bounds__(128) head_prepare_kernel(
             inv = 1.0f / sqrtf(ss / (float)hd + eps);
         }
         if (vec) {
-            for (int d = lane * 4; d < hd; d += 128) {
-                float4 a = mul4(*(const float4*)(src + d), inv);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int d = lane * 4 + k * 128;
+                if (d >= hd) break;
+                float4 a = mul4(held[k], inv);
                 if (nw) a = mul4(a, *(const float4*)(nw + d));
                 if (d < rot) {
                     const bool low = d < half;
